@@ -13,17 +13,11 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import CacheView, CompositeNeed, FixedStateNeed, PagedKVNeed
+from ..parts.base import CacheView, CompositeNeed, FixedStateNeed, PagedKVNeed, SharedPagesNeed, need_leaves
 from .manager import GroupSpec
 
 
-def leaves(need) -> list:
-    """The paged / fixed-state needs that a run's need is made of (a composite's entries, flattened in order)."""
-    if need is None:
-        return []
-    if isinstance(need, CompositeNeed):
-        return [leaf for sub in need.parts for leaf in leaves(sub)]
-    return [need]
+leaves = need_leaves
 
 
 @dataclass
@@ -65,7 +59,7 @@ class CacheLayout:
         for need, groups in zip(self.needs, self.leaf_group):
             for leaf, g in zip(leaves(need), groups):
                 if g is not None:
-                    out[g] += 2 * leaf.num_kv_heads * page_size * leaf.row_dim * item
+                    out[g] += leaf.planes * leaf.num_kv_heads * page_size * leaf.row_dim * item
         return out
 
     def state_bytes_per_slot(self, dtype: torch.dtype) -> int:
@@ -98,8 +92,10 @@ class CacheStorage:
             mine = []
             for leaf, g in zip(leaves(need), groups):
                 if isinstance(leaf, PagedKVNeed):
-                    mine.append((torch.full((num_pages[g], 2, leaf.num_kv_heads, page_size, leaf.row_dim), fill,
+                    mine.append((torch.full((num_pages[g], leaf.planes, leaf.num_kv_heads, page_size, leaf.row_dim), fill,
                                             dtype=dtype, device=device), None))
+                elif isinstance(leaf, SharedPagesNeed):
+                    mine.append((None, None))
                 else:
                     sdt = torch.float32 if leaf.dtype == "float32" else dtype
                     mine.append((None, torch.full((max(num_state_slots, 1), *leaf.shape), fill, dtype=sdt,
@@ -109,24 +105,25 @@ class CacheStorage:
             self.states.append(next((s for _, s in mine if s is not None), None))
 
     def view(self, run: int, cache_from: int | None, batch) -> CacheView:
-        src = run if cache_from is None else cache_from
-        writes = cache_from is None
-        need = self.layout.needs[src]
-        if not isinstance(need, CompositeNeed):
-            g = self.layout.run_group[src]
-            return CacheView(pages=self.pages[src], tables=batch.groups[g] if g is not None else None,
-                             writes=writes, state=self.states[src])
-        flat = iter(zip(self.leaf_tensors[src], self.layout.leaf_group[src]))
+        """What run ``run`` sees: its own pages and states; where it reads the pages of run ``cache_from``, those
+        pages (in their order among that run's paged entries) with ``writes`` False."""
+        own = iter(zip(self.leaf_tensors[run], self.layout.leaf_group[run]))
+        lent = iter(()) if cache_from is None else iter(
+            [(pair[0], g) for pair, g in zip(self.leaf_tensors[cache_from], self.layout.leaf_group[cache_from])
+             if pair[0] is not None])
 
         def build(n) -> CacheView:
             if isinstance(n, CompositeNeed):
-                return CacheView(writes=writes, children=tuple(build(sub) for sub in n.parts))
+                return CacheView(children=tuple(build(sub) for sub in n.parts))
             if n is None:
-                return CacheView(writes=writes)
-            (pages, state), g = next(flat)
-            return CacheView(pages=pages, tables=batch.groups[g] if g is not None else None, writes=writes, state=state)
+                return CacheView()
+            (pages, state), g = next(own)
+            if isinstance(n, SharedPagesNeed):
+                pages, g = next(lent)
+                return CacheView(pages=pages, tables=batch.groups[g], writes=False)
+            return CacheView(pages=pages, tables=batch.groups[g] if g is not None else None, state=state)
 
-        return build(need)
+        return build(self.layout.needs[run])
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for mine in self.leaf_tensors for pair in mine for t in pair

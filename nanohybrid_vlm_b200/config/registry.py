@@ -21,20 +21,26 @@ class ArchitectureEntry:
     model_types: tuple[str, ...]
     parse_config: Callable[[dict], ModelConfig]
     build_spec: Callable[[ModelConfig], "ModelSpec"]  # noqa: F821
+    # (raw config.json, shape_of) -> raw config.json completed by sizes that only a checkpoint tensor's shape gives;
+    # shape_of(name) is the shape of that tensor in the model folder, or None.  None: config.json says everything.
+    complete_config: Callable[[dict, Callable], dict] | None = None
 
 
 class ArchitectureRegistry:
     def __init__(self):
         self._entries: dict[str, ArchitectureEntry] = {}
 
-    def register(self, name: str, *, model_types, parse_config, build_spec, replace: bool = False) -> None:
+    def register(self, name: str, *, model_types, parse_config, build_spec, replace: bool = False,
+                 complete_config=None) -> None:
         if not name:
             raise ValueError("an architecture needs a name")
         if name in self._entries and not replace:
             raise ValueError(f"architecture {name!r} is already registered")
         if not callable(parse_config) or not callable(build_spec):
             raise TypeError(f"architecture {name!r}: parse_config and build_spec must be callable")
-        self._entries[name] = ArchitectureEntry(name, tuple(model_types), parse_config, build_spec)
+        if complete_config is not None and not callable(complete_config):
+            raise TypeError(f"architecture {name!r}: complete_config must be callable")
+        self._entries[name] = ArchitectureEntry(name, tuple(model_types), parse_config, build_spec, complete_config)
 
     def unregister(self, name: str) -> None:
         self._entries.pop(name, None)
@@ -63,9 +69,34 @@ class ArchitectureRegistry:
 ARCHITECTURES = ArchitectureRegistry()
 
 
-def register_architecture(name: str, *, model_types=(), parse_config, build_spec, replace=False) -> None:
+def register_architecture(name: str, *, model_types=(), parse_config, build_spec, replace=False,
+                          complete_config=None) -> None:
     ARCHITECTURES.register(name, model_types=model_types, parse_config=parse_config,
-                           build_spec=build_spec, replace=replace)
+                           build_spec=build_spec, replace=replace, complete_config=complete_config)
+
+
+def checkpoint_shapes(model_dir: str) -> dict[str, tuple[int, ...]]:
+    """Name -> shape of every tensor in the folder's ``*.safetensors`` files, from their headers alone (8 bytes of
+    little-endian length, then that many bytes of JSON).  A folder without such files gives an empty table."""
+    import glob
+    import json
+    import os
+    import struct
+    shapes: dict[str, tuple[int, ...]] = {}
+    for path in sorted(glob.glob(os.path.join(model_dir, "*.safetensors"))):
+        with open(path, "rb") as f:
+            head = f.read(8)
+            if len(head) != 8:
+                raise ConfigError(f"{path}: too short for a safetensors file")
+            (n,) = struct.unpack("<Q", head)
+            try:
+                table = json.loads(f.read(n))
+            except (json.JSONDecodeError, UnicodeDecodeError) as e:
+                raise ConfigError(f"{path}: the header is not valid JSON: {e}") from e
+        for name, info in table.items():
+            if name != "__metadata__" and isinstance(info, dict) and "shape" in info:
+                shapes[name] = tuple(int(x) for x in info["shape"])
+    return shapes
 
 
 def load_model_config(model_dir: str) -> tuple[ArchitectureEntry, ModelConfig]:
@@ -73,4 +104,7 @@ def load_model_config(model_dir: str) -> tuple[ArchitectureEntry, ModelConfig]:
     from .. import models  # noqa: F401  (registers the built-in architecture)
     raw = read_config_json(model_dir)
     entry = ARCHITECTURES.resolve(raw)
+    if entry.complete_config is not None:
+        shapes = checkpoint_shapes(model_dir)
+        raw = entry.complete_config(raw, shapes.get)
     return entry, entry.parse_config(raw)

@@ -22,6 +22,9 @@
 // `row` >= max(d, dv) elements and each kind uses its leading ones), and a sink per query head: a number that joins
 // the softmax denominator as exp(sink) with no key, no value and no scale, counted once.  It enters as the start
 // of the running maximum and sum (m = sink, l = 1), which later chunks rescale like any other term.
+// Two more: a bias by distance, score - slopes[head] * (query position - key position), and pages with one plane
+// (planes == 1): a row of such a page is the key, and its leading dv elements are the value as well (keys and
+// values that are one latent vector per token, stored once).
 #include <math.h>
 
 #include "nhv_common.cuh"
@@ -39,7 +42,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
                                        int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                        int n_seqs, int nq, int nkv, int d, int page_size, int n_pages, int window,
                                        float scale, int TQ, int GS, int dv, int row, const float* __restrict__ sinks,
-                                       int chunk) {
+                                       int chunk, const float* __restrict__ slopes, int planes) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int G = nq / nkv;
@@ -119,9 +122,9 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
         const int j = c0 + r;
         const int page = block_table[(size_t)seq * bt_stride + j / page_size];
         const int off = j % page_size;
-        const size_t base = ((((size_t)page * 2) * nkv + kvh) * page_size + off) * row + c;
+        const size_t base = ((((size_t)page * planes) * nkv + kvh) * page_size + off) * row + c;
         if (c < d) kx = to_f32<T>(kv_pages[base]);
-        if (c < dv) vx = to_f32<T>(kv_pages[base + (size_t)nkv * page_size * row]);
+        if (c < dv) vx = planes == 2 ? to_f32<T>(kv_pages[base + (size_t)nkv * page_size * row]) : (c < d ? kx : 0.f);
       }
       if (c < d) Ks[r * ks + c] = kx;
       if (c < dv) Vs[r * dv + c] = vx;
@@ -144,6 +147,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
         float acc = 0.f;
         for (int c = 0; c < d; ++c) acc = fmaf(qv[c], kv[c], acc);
         s = acc * scale;
+        if (slopes) s -= slopes[kvh * G + g0 + (p - tq * gs)] * (float)(pos - j);
       }
       const float cmax = warp_max(s);
       if (cmax == -INFINITY) continue;
@@ -189,13 +193,14 @@ NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* 
                                   const void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
                                   const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int dv, int row,
                                   int page_size, int n_pages, int window, int chunk, float scale, const float* sinks,
-                                  cudaStream_t stream) {
+                                  const float* slopes, int planes, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   NHV_REQUIRE(d > 0 && d <= AT_MAX_D && dv > 0 && dv <= AT_MAX_D, "attention: head sizes %d / %d are beyond the supported %d",
               d, dv, AT_MAX_D);
   NHV_REQUIRE(row >= d && row >= dv, "attention: a page row of %d elements does not hold a head of %d / %d", row, d, dv);
   NHV_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
+  NHV_REQUIRE(planes == 2 || (planes == 1 && dv <= d), "attention: pages have a key and a value plane, or one plane whose rows' leading elements are the values");
   const int G = nq / nkv;
   const int GS = G < 8 ? G : 8;
   const int TQ = AT_MAX_PAIRS / GS;
@@ -210,7 +215,7 @@ NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* 
                                     (int)smem), "attention");                                                  \
     nhv_launch(attn_paged_simt_kernel<T>, grid, AT_WARPS * 32, smem, stream,                                   \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,  \
-        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk);                      \
+        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk, slopes, planes);      \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
@@ -225,5 +230,5 @@ NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out
                                const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int page_size,
                                int n_pages, int window, float scale, cudaStream_t stream) {
   return nhv_attention_simt_ex(dtype, q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len,
-                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, 0, scale, nullptr, stream);
+                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, 0, scale, nullptr, nullptr, 2, stream);
 }

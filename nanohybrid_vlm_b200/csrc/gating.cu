@@ -133,3 +133,81 @@ NHV_API int nhv_clamped_glu(int dtype, void* out, const void* gate_up, int n_row
   NHV_CHECK_LAUNCH("clamped_glu");
   return 0;
 }
+
+// out[t, c] = x[t, c] * sigmoid(g[t, c / group]): one gate per head of `group` columns.  out may be x itself.
+template <typename T>
+__global__ void sigmoid_mul_heads_kernel(T* out, int out_stride, const T* x, int x_stride, const T* __restrict__ g,
+                                         int g_stride, int width, int group, size_t total) {
+  pdl_prologue();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width;
+    const int c = (int)(i - t * width);
+    out[t * out_stride + c] = from_f32<T>(to_f32<T>(x[t * x_stride + c]) * sigmoid_f(to_f32<T>(g[t * g_stride + c / group])));
+  }
+}
+
+NHV_API int nhv_sigmoid_mul_heads(int dtype, void* out, int out_stride, const void* x, int x_stride, const void* g,
+                                  int g_stride, int n_rows, int width, int group, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NHV_REQUIRE(n_rows > 0 && width > 0 && group > 0 && width % group == 0, "sigmoid_mul_heads: %d columns do not divide into heads of %d", width, group);
+  const size_t total = (size_t)n_rows * width;
+  if (dtype == NHV_F32)
+    nhv_launch(sigmoid_mul_heads_kernel<float>, gating_blocks(total), 256, 0, stream, (float*)out, out_stride, (const float*)x,
+               x_stride, (const float*)g, g_stride, width, group, total);
+  else if (dtype == NHV_BF16)
+    nhv_launch(sigmoid_mul_heads_kernel<__nv_bfloat16>, gating_blocks(total), 256, 0, stream, (__nv_bfloat16*)out, out_stride,
+               (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)g, g_stride, width, group, total);
+  else
+    NHV_REQUIRE(false, "sigmoid_mul_heads: unknown dtype %d", dtype);
+  NHV_CHECK_LAUNCH("sigmoid_mul_heads");
+  return 0;
+}
+
+// x = max(x, 0)^2 in place, computed in fp32 and rounded once (the unit of a feed-forward without a gate).
+template <typename T, int VEC>
+__global__ void relu_squared_kernel(T* __restrict__ x, size_t total) {
+  pdl_prologue();
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < total; i += (size_t)gridDim.x * blockDim.x * VEC) {
+    if constexpr (VEC == 8) {
+      float v[8];
+      nhv_load8(v, x + i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float p = fmaxf(v[e], 0.f);
+        v[e] = p * p;
+      }
+      nhv_store8(x + i, v);
+    } else {
+      const float p = fmaxf(to_f32<T>(x[i]), 0.f);
+      x[i] = from_f32<T>(p * p);
+    }
+  }
+}
+
+NHV_API int nhv_relu_squared(int dtype, void* x, size_t total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const bool vec = total % 8 == 0 && aligned16(x);
+#define GO(T, V) nhv_launch(relu_squared_kernel<T, V>, gating_blocks(total / V), 256, 0, stream, (T*)x, total)
+  if (dtype == NHV_F32) { if (vec) GO(float, 8); else GO(float, 1); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
+  else NHV_REQUIRE(false, "relu_squared: unknown dtype %d", dtype);
+#undef GO
+  NHV_CHECK_LAUNCH("relu_squared");
+  return 0;
+}
+
+// Logits in place (fp32): z <- z * scale, then, with cap > 0, z <- cap * tanh(z / cap).
+__global__ void scale_softcap_kernel(float* __restrict__ z, float scale, float cap, size_t total) {
+  pdl_prologue();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = z[i] * scale;
+    z[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+NHV_API int nhv_scale_softcap(float* z, float scale, float cap, size_t total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  nhv_launch(scale_softcap_kernel, gating_blocks(total), 256, 0, stream, z, scale, cap, total);
+  NHV_CHECK_LAUNCH("scale_softcap");
+  return 0;
+}

@@ -11,10 +11,13 @@ constexpr int GM = 64, GN = 64, GK = 16;
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256) gemm_nt_simt_kernel(TO* __restrict__ C, const T* __restrict__ A,
                                                            const T* __restrict__ W, int M, int N, int K, int lda,
-                                                           int ldw, int ldc) {
+                                                           int ldw, int ldc, long batch_a, long batch_w, long batch_c) {
   __shared__ __align__(16) float As[GK][GM + 4];
   __shared__ __align__(16) float Ws[GK][GN + 4];
   pdl_prologue();
+  A += (size_t)blockIdx.z * batch_a;                     // one product per blockIdx.z, the operands a fixed step apart
+  W += (size_t)blockIdx.z * batch_w;
+  C += (size_t)blockIdx.z * batch_c;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 4 x 4 outputs each
   const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
   float acc[4][4];
@@ -65,23 +68,31 @@ __global__ void __launch_bounds__(256) gemm_nt_simt_kernel(TO* __restrict__ C, c
 }
 
 // out_f32 != 0: C is fp32 whatever the storage type of A and W (logits).
-NHV_API int nhv_gemm_nt_simt(int dtype, void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
-                             int ldc, int out_f32, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
+// `batch` products in one launch: product b reads A + b * batch_a, W + b * batch_w and writes C + b * batch_c (in
+// elements); the operands of different products may interleave (heads side by side in a row).
+NHV_API int nhv_gemm_nt_simt_batched(int dtype, void* C, const void* A, const void* W, int M, int N, int K, int lda,
+                                     int ldw, int ldc, int out_f32, int batch, long batch_a, long batch_w,
+                                     long batch_c, cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
   NHV_REQUIRE(M > 0 && N > 0 && K > 0 && lda >= K && ldw >= K && ldc >= N, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-  dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
-  NHV_REQUIRE(grid.y <= 65535, "gemm: M=%d is beyond the grid's reach", M);
+  dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM, batch);
+  NHV_REQUIRE(grid.y <= 65535 && batch > 0 && batch <= 65535, "gemm: M=%d or %d products are beyond the grid's reach", M, batch);
   if (dtype == NHV_F32)
     nhv_launch(gemm_nt_simt_kernel<float, float>, grid, 256, 0, stream, (float*)C, (const float*)A, (const float*)W, M, N,
-               K, lda, ldw, ldc);
+               K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else if (dtype == NHV_BF16 && out_f32)
     nhv_launch(gemm_nt_simt_kernel<__nv_bfloat16, float>, grid, 256, 0, stream, (float*)C, (const __nv_bfloat16*)A,
-               (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
+               (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else if (dtype == NHV_BF16)
     nhv_launch(gemm_nt_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, (__nv_bfloat16*)C,
-               (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc);
+               (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else
     NHV_REQUIRE(false, "gemm: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("gemm_nt_simt");
   return 0;
+}
+
+NHV_API int nhv_gemm_nt_simt(int dtype, void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                             int ldc, int out_f32, cudaStream_t stream) {
+  return nhv_gemm_nt_simt_batched(dtype, C, A, W, M, N, K, lda, ldw, ldc, out_f32, 1, 0, 0, 0, stream);
 }

@@ -7,6 +7,7 @@
 //   k heads: the same -> the token's slot of the K pages
 //   v heads: copied -> the token's slot of the V pages
 // eps < 0 leaves the norm out.  Rotation and norm are computed in fp32 and rounded once.
+// q_weight / k_weight (optional, [dk], shared by the heads of their kind): the normed head times this weight.
 // bias (optional, [nq*dk + nkv*dk], the query and key columns of qkv): added in fp32 to what the projection gave,
 // before anything else (projected values have none).  v_from_k: the values are the key heads as projected (with their bias, before the rotation); qkv
 // then has no value columns and dv == dk.
@@ -24,7 +25,8 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
                                        const float* __restrict__ cos_sin, int rotary_dim, int max_position,
                                        int n_tokens, int nq, int nkv, int dk, int dv, int row, int page_size,
                                        int n_pages, float eps, int heads_per_token, const T* __restrict__ bias,
-                                       int v_from_k) {
+                                       int v_from_k, const T* __restrict__ q_weight,
+                                       const T* __restrict__ k_weight) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,10 +82,11 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
     }
     ss = warp_sum(ss);
     const float r = eps >= 0.f ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    const T* hw = kind == 0 ? q_weight : k_weight;
 #pragma unroll
     for (int k = 0; k < RN_MAX_D / 32; ++k) {
       const int c = lane + k * 32;
-      if (c < d) dst[c] = from_f32<T>(mine[k] * r);
+      if (c < d) dst[c] = from_f32<T>(hw ? mine[k] * r * to_f32<T>(hw[c]) : mine[k] * r);
     }
   } else {
     for (int c = lane; c < d; c += 32) dst[c] = from_f32<T>(v[c]);
@@ -95,7 +98,7 @@ NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void
                                 void* kv_pages, const int* slot_mapping, const int* positions, const float* cos_sin,
                                 int rotary_dim, int max_position, int n_tokens, int nq, int nkv, int dk, int dv, int row,
                                 int page_size, int n_pages, float eps, const void* bias, int v_from_k,
-                                cudaStream_t stream) {
+                                const void* q_weight, const void* k_weight, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(n_tokens > 0 && nq > 0 && nkv >= 0 && dk > 0 && dv > 0, "rope_norm_store: bad sizes");
   NHV_REQUIRE(dk <= RN_MAX_D && dv <= RN_MAX_D, "rope_norm_store: head sizes %d / %d are beyond the supported %d", dk, dv, RN_MAX_D);
@@ -112,7 +115,8 @@ NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void
 #define LAUNCH(T)                                                                                                  \
   nhv_launch(rope_norm_store_kernel<T>, blocks, RN_WARPS * 32, smem, stream, (const T*)qkv, qkv_stride, (T*)q_out, \
              q_out_stride, (T*)kv_pages, slot_mapping, positions, cos_sin, rotary_dim, max_position, n_tokens, nq, \
-             nkv, dk, dv, row, page_size, n_pages, eps, heads_per_token, (const T*)bias, v_from_k)
+             nkv, dk, dv, row, page_size, n_pages, eps, heads_per_token, (const T*)bias, v_from_k, (const T*)q_weight,    \
+             (const T*)k_weight)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
   else NHV_REQUIRE(false, "rope_norm_store: unknown dtype %d", dtype);

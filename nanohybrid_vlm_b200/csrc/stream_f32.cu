@@ -5,6 +5,8 @@
 //                      stream[src] = s                                         (if write_stream)
 //                      out[r] = s / sqrt(mean(s^2) + eps) * (w + weight_offset), rounded once to the storage type
 //                      src = rows[r] or r
+//                      groups > 1: the row is cut into that many equal consecutive parts and each part is divided
+//                      by the root mean square of its own elements
 // One block per row; the row of fp32 sums lives in shared memory between the two passes.
 #include "nhv_common.cuh"
 
@@ -41,7 +43,7 @@ __global__ void rmsnorm_stream_kernel(T* __restrict__ out, const T* __restrict__
                                       const T* __restrict__ a2, float c0, float c1, float c2,
                                       float* __restrict__ stream, const T* __restrict__ w,
                                       const int* __restrict__ rows, int width, float eps, int write_stream,
-                                      float weight_offset) {
+                                      float weight_offset, int groups) {
   extern __shared__ float row[];
   __shared__ float red[33];
   pdl_prologue();
@@ -60,18 +62,34 @@ __global__ void rmsnorm_stream_kernel(T* __restrict__ out, const T* __restrict__
     row[c] = s;
     ss = fmaf(s, s, ss);
   }
+  T* dst = out + (size_t)r * width;
+  if (groups > 1) {
+    // one warp per part in turn: the part's sum of squares in a fixed order, then its outputs
+    __syncthreads();
+    const int part = width / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    for (int g = warp; g < groups; g += nwarp) {
+      const float* pr = row + (size_t)g * part;
+      float sg = 0.f;
+      for (int c = lane; c < part; c += 32) sg = fmaf(pr[c], pr[c], sg);
+      sg = warp_sum(sg);
+      const float rg = 1.0f / sqrtf(sg / (float)part + eps);
+      for (int c = lane; c < part; c += 32)
+        dst[g * part + c] = from_f32<T>(pr[c] * rg * (to_f32<T>(w[g * part + c]) + weight_offset));
+    }
+    return;
+  }
   const float total = block_sum(ss, red);
   const float rstd = 1.0f / sqrtf(total / (float)width + eps);
-  T* dst = out + (size_t)r * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x)
     dst[c] = from_f32<T>(row[c] * rstd * (to_f32<T>(w[c]) + weight_offset));
 }
 
 NHV_API int nhv_rmsnorm_stream(int dtype, void* out, const void* a0, const void* a1, const void* a2, float c0, float c1,
                                float c2, float* stream_rows, const void* w, const int* rows, int n_rows, int width,
-                               float eps, int write_stream, float weight_offset, cudaStream_t stream) {
+                               float eps, int write_stream, float weight_offset, int groups, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NHV_REQUIRE(n_rows > 0 && width > 0 && stream_rows && out && w, "rmsnorm_stream: bad arguments");
+  NHV_REQUIRE(groups >= 1 && width % groups == 0, "rmsnorm_stream: a row of %d does not divide into %d parts", width, groups);
   NHV_REQUIRE((a0 || !a1) && (a1 || !a2), "rmsnorm_stream: addends are given in order");
   NHV_REQUIRE(!(rows && write_stream), "rmsnorm_stream: a gathered norm cannot write the stream back");
   const size_t smem = (size_t)width * sizeof(float);
@@ -84,7 +102,7 @@ NHV_API int nhv_rmsnorm_stream(int dtype, void* out, const void* a0, const void*
       NHV_CUDA(cudaFuncSetAttribute(rmsnorm_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
                                     (int)smem), "rmsnorm_stream");                                              \
     nhv_launch(rmsnorm_stream_kernel<T>, n_rows, threads, smem, stream, (T*)out, (const T*)a0, (const T*)a1,    \
-               (const T*)a2, c0, c1, c2, stream_rows, (const T*)w, rows, width, eps, write_stream, weight_offset); \
+               (const T*)a2, c0, c1, c2, stream_rows, (const T*)w, rows, width, eps, write_stream, weight_offset, groups); \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);

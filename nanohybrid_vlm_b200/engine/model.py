@@ -12,7 +12,8 @@ from dataclasses import dataclass, replace
 import torch
 
 from .. import parts as _registered_parts  # noqa: F401  (importing the package registers the built-in parts)
-from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, FixedStateNeed, PagedKVNeed, Part
+from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, FixedStateNeed, PagedKVNeed, Part, need_leaves,
+                          with_shared_pages)
 from ..parts.spec import ModelSpec, ParamDecl, PartUse
 
 
@@ -101,18 +102,18 @@ class CausalLM:
 
     # ------------------------------------------------------------------ cache needs
     def cache_needs(self) -> list[PagedKVNeed | FixedStateNeed | None]:
-        """For every run of the order: what its mixer keeps between steps (None: nothing, or it reads
-        another run's cache)."""
+        """For every run of the order: what its layer keeps between steps (None: nothing).  A run that reads another
+        run's pages keeps none of its own (:class:`SharedPagesNeed` stands in their place); fixed-size state stays
+        its own."""
         needs = []
         for run in self.spec.order:
-            owner = self.blocks[run.layer].cache_owner
-            need = owner.cache_need() if owner is not None else None
+            need = self.blocks[run.layer].cache_need()
             if run.cache_from is not None:
-                src_owner = self.blocks[self.spec.order[run.cache_from].layer].cache_owner
-                src = src_owner.cache_need() if src_owner is not None else None
-                if need != src:
+                src = self.blocks[self.spec.order[run.cache_from].layer].cache_need()
+                mine, theirs = ([n for n in need_leaves(x) if isinstance(n, PagedKVNeed)] for x in (need, src))
+                if not mine or mine != theirs:
                     raise ValueError(f"a run reads the cache of run {run.cache_from}, whose shape differs from its own")
-                need = None
+                need = with_shared_pages(need)
             needs.append(need)
         return needs
 

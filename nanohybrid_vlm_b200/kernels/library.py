@@ -36,13 +36,13 @@ _SIGNATURES = {
     "nhv_gelu_tanh_mul": [I, P, P, I, I, P],
     "nhv_gemm_rows_f32": [P, I, P, I, P, I, I, I, I, P],
     "nhv_embed_scaled_f32": [I, P, P, P, I, I, I, F, P],
-    "nhv_rmsnorm_stream": [I, P, P, P, P, F, F, F, P, P, P, I, I, F, I, F, P],
+    "nhv_rmsnorm_stream": [I, P, P, P, P, F, F, F, P, P, P, I, I, F, I, F, I, P],
     "nhv_scaled_sum": [I, P, P, P, F, F, c_size_t, P],
     "nhv_short_conv_silu": [I, I, P, I, P, I, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
     "nhv_delta_rule": [I, P, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P],
     "nhv_ssd_scan": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, I, I, P],
     "nhv_gated_rmsnorm": [I, P, I, P, P, I, P, I, I, I, I, F, I, I, P],
-    "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, I, P],
+    "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, I, P, P, P],
     "nhv_dyntanh": [I, I, I, P, P, P, P, P, I, I, P],
     "nhv_embed_dyntanh": [I, P, P, P, P, P, P, I, I, I, P],
     "nhv_dyntanh_stream": [I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
@@ -57,7 +57,14 @@ _SIGNATURES = {
     "nhv_moe_gather_rows": [P, P, P, I, I, I, P],
     "nhv_moe_gemm_tcgen05": [I, P, P, P, P, I, P, P, I, I, I, F, F, P],
     "nhv_moe_combine": [I, P, P, P, P, P, I, P, P, P, I, I, I, I, P],
-    "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P],
+    "nhv_causal_filter_add": [I, P, P, I, P, I, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
+    "nhv_latent_rope_store": [I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "nhv_gemm_nt_simt_batched": [I, P, P, P, I, I, I, I, I, I, I, I, ctypes.c_long, ctypes.c_long, ctypes.c_long, P],
+    "nhv_general_delta": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, I, I, I, I, I, F, P],
+    "nhv_sigmoid_mul_heads": [I, P, I, P, I, P, I, I, I, I, P],
+    "nhv_relu_squared": [I, P, c_size_t, P],
+    "nhv_scale_softcap": [P, F, F, c_size_t, P],
 }
 
 

@@ -111,10 +111,11 @@ def embed_scaled_f32(out, table, ids, scale: float) -> None:
 
 
 def rmsnorm_stream(out, stream, weight, eps: float, addends=(), rows=None, write_stream: bool = True,
-                   weight_offset: float = 0.0) -> None:
+                   weight_offset: float = 0.0, groups: int = 1) -> None:
     """The norm over a float32 residual stream [T, width]: s = stream[src] + sum(coef * tensor[src]) in 32-bit over up
     to three ``addends`` (tensor in the storage type, coef), written back to the stream unless ``rows`` gathers, and
-    out[r] = s / rms(s) * (weight + weight_offset) rounded once to the storage type; src = rows[r] or r."""
+    out[r] = s / rms(s) * (weight + weight_offset) rounded once to the storage type; src = rows[r] or r.  ``groups``
+    > 1: the row is cut into that many equal consecutive parts, each divided by its own root mean square."""
     tensors = [t for t, _ in addends]
     _need_cuda(out, stream, weight, rows, *tensors)
     _contig("out", out); _contig("stream", stream)
@@ -131,7 +132,7 @@ def rmsnorm_stream(out, stream, weight, eps: float, addends=(), rows=None, write
     coefs = [float(c) for _, c in addends] + [0.0] * (3 - len(tensors))
     call("nhv_rmsnorm_stream", dtype_code(out), out.data_ptr(), *ptrs, *coefs, stream.data_ptr(), weight.data_ptr(),
          _ptr(rows), n_rows, width, float(eps), int(bool(write_stream and tensors and rows is None)),
-         float(weight_offset), stream_ptr())
+         float(weight_offset), int(groups), stream_ptr())
 
 
 def scaled_sum(out, a, b, ca: float, cb: float) -> None:
@@ -258,6 +259,114 @@ def dyntanh_stream(out, stream, pre, addend=None, post=None, rows=None, write_st
     call("nhv_dyntanh_stream", dtype_code(out), out.data_ptr(), stream.data_ptr(), _ptr(addend), _ptr(pp[0]), _ptr(pp[1]),
          _ptr(pp[2]), pre[0].data_ptr(), pre[1].data_ptr(), pre[2].data_ptr(), _ptr(rows), n_rows, width,
          int(bool(write_stream and addend is not None and rows is None)), stream_ptr())
+
+
+def causal_filter_add(out1, out2, x, w1, w2, state, batch) -> None:
+    """out1 [T, C] = x + (causal filter over time of x with w1 [C, K], no bias, no activation); out2 likewise with w2
+    (both None: one filter).  ``state`` [slots, (K - 1) * C] float32 holds each request's last K - 1 inputs, serves both
+    filters and is moved on."""
+    _need_cuda(out1, out2, x, w1, w2, state)
+    C, K = w1.shape
+    assert x.dim() == 2 and x.shape[1] == C and x.is_contiguous() and out1.shape == x.shape and out1.is_contiguous()
+    assert x.dtype == w1.dtype == out1.dtype and w1.is_contiguous() and (out2 is None) == (w2 is None)
+    assert out2 is None or (out2.shape == x.shape and out2.is_contiguous() and out2.dtype == x.dtype
+                            and w2.shape == w1.shape and w2.dtype == w1.dtype and w2.is_contiguous())
+    assert K == 1 or (state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1)
+    call("nhv_causal_filter_add", dtype_code(x), out1.data_ptr(), _ptr(out2), C, x.data_ptr(), C, w1.data_ptr(), _ptr(w2),
+         _ptr(state) if K > 1 else None, state.stride(0) if K > 1 else 0, batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+         batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
+
+
+def latent_rope_store(kv, q, q_lat, pages, slot_mapping, positions, cos_sin, rotary_dim: int, H: int, dn: int, dr: int,
+                      rank: int, eps: float, weight) -> None:
+    """For attention over one latent vector per token.  kv [T, rank + dr] (a view with unit column stride): the first
+    ``rank`` elements normed (unit root mean square, times ``weight`` [rank]) and the last dr rotated go to the token's
+    row of ``pages`` [pages, 1, 1, page_size, row >= rank + dr] (None: nothing is stored).  q [T, H * (dn + dr)]: every
+    head's last dr elements, rotated, go to q_lat [T, H * (rank + dr)] behind the head's first ``rank`` places."""
+    _need_cuda(kv, q, q_lat, pages, slot_mapping, positions, cos_sin, weight)
+    T = kv.shape[0]
+    assert kv.stride(1) == 1 and kv.shape[1] == rank + dr and q.stride(1) == 1 and q.shape == (T, H * (dn + dr))
+    assert q_lat.stride(1) == 1 and q_lat.shape == (T, H * (rank + dr)) and kv.dtype == q.dtype == q_lat.dtype == weight.dtype
+    assert weight.is_contiguous() and weight.numel() == rank
+    if pages is not None:
+        _contig("pages", pages)
+        n_pages, planes, heads, page_size, row = pages.shape
+        assert planes == 1 and heads == 1 and row >= rank + dr and pages.dtype == kv.dtype
+        assert slot_mapping.dtype == torch.int32 and slot_mapping.numel() >= T
+    else:
+        n_pages, page_size, row = 0, 0, rank + dr
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == rotary_dim
+        assert positions.dtype == torch.int32
+    call("nhv_latent_rope_store", dtype_code(kv), kv.data_ptr(), kv.stride(0), q.data_ptr(), q.stride(0), q_lat.data_ptr(),
+         q_lat.stride(0), _ptr(pages), _ptr(slot_mapping), _ptr(positions), _ptr(cos_sin), int(rotary_dim),
+         0 if cos_sin is None else cos_sin.shape[0], T, H, dn, dr, rank, row, page_size, n_pages, float(eps),
+         weight.data_ptr(), stream_ptr())
+
+
+def linear_heads(out, x, weight) -> None:
+    """One product per head: out[:, h, :] = x[:, h, :] @ weight[h]^T for x [T, H, K], weight [H, N, K] (contiguous),
+    out [T, H, N]; x and out may be views into wider rows (heads a fixed step apart, unit stride inside a head).
+    float32 runs the fixed-order CUDA-core product; bfloat16 the library's batched product."""
+    _need_cuda(out, x, weight)
+    _contig("weight", weight)
+    T, H, K = x.shape
+    N = weight.shape[1]
+    assert weight.shape == (H, N, K) and out.shape == (T, H, N) and x.dtype == weight.dtype == out.dtype
+    assert x.stride(2) == 1 and out.stride(2) == 1
+    if x.dtype == torch.bfloat16 and T > LINEAR_HEADS_SIMT_ROWS:
+        library.LAUNCHES += 1
+        torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    call("nhv_gemm_nt_simt_batched", dtype_code(x), out.data_ptr(), x.data_ptr(), weight.data_ptr(), T, N, K, x.stride(0),
+         K, out.stride(0), 0, H, x.stride(1), N * K, out.stride(1), stream_ptr())
+
+
+LINEAR_HEADS_SIMT_ROWS = 1 << 30    # tokens up to which the per-head products in bfloat16 run on the CUDA cores
+
+
+def general_delta(o, proj, aw, a_bias, w2, w0, state, batch, H: int, d: int, decay_floor: float) -> None:
+    """The generalised delta rule over the step's tokens.  proj [T, >= 3 H d] (r, k, v in the storage type), aw
+    [T, H d + rank] float32 (the removal rate's projection, then the decay's inner projection), a_bias / w0 [H d] and
+    w2 [H d, rank] in the storage type, state [slots, H d d] float32 -> o [T, H d] float32 (before its norm and gate).
+    The decay per key channel is exp(-decay_floor * sigmoid(w2 tanh(inner) + w0))."""
+    _need_cuda(o, proj, aw, a_bias, w2, w0, state)
+    T, n = proj.shape[0], H * d
+    rank = w2.shape[1]
+    assert proj.stride(1) == 1 and proj.shape[1] >= 3 * n and aw.dtype == torch.float32 and aw.stride(1) == 1
+    assert aw.shape == (T, n + rank) and o.dtype == state.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, n)
+    assert a_bias.dtype == w2.dtype == w0.dtype == proj.dtype and w2.is_contiguous() and w2.shape == (n, rank)
+    assert a_bias.numel() == n and w0.numel() == n and state.stride(1) == 1
+    scratch = torch.empty(T * (6 * n + 2 * H), dtype=torch.float32, device=proj.device)
+    vec, v32, sc = scratch.data_ptr(), scratch.data_ptr() + 4 * 5 * T * n, scratch.data_ptr() + 4 * 6 * T * n
+    call("nhv_general_delta", dtype_code(proj), o.data_ptr(), proj.data_ptr(), proj.stride(0), aw.data_ptr(), aw.stride(0),
+         a_bias.data_ptr(), w2.data_ptr(), w0.data_ptr(), state.data_ptr(), state.stride(0), vec, sc, v32,
+         batch.cu_q.data_ptr(), batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, d, rank,
+         float(decay_floor), stream_ptr())
+
+
+def sigmoid_mul_heads(out, x, gate, group: int) -> None:
+    """out[t, c] = x[t, c] * sigmoid(gate[t, c // group]): one gate per head of ``group`` columns, in 32-bit."""
+    _need_cuda(out, x, gate)
+    assert out.shape == x.shape and out.dim() == 2 and out.dtype == x.dtype == gate.dtype and x.shape[1] % group == 0
+    assert gate.shape == (x.shape[0], x.shape[1] // group) and out.stride(1) == x.stride(1) == gate.stride(1) == 1
+    call("nhv_sigmoid_mul_heads", dtype_code(out), out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), gate.data_ptr(),
+         gate.stride(0), x.shape[0], x.shape[1], int(group), stream_ptr())
+
+
+def relu_squared(x) -> None:
+    """x = max(x, 0) ** 2 in place."""
+    _need_cuda(x)
+    _contig("x", x)
+    call("nhv_relu_squared", dtype_code(x), x.data_ptr(), x.numel(), stream_ptr())
+
+
+def scale_softcap(logits, scale: float, cap: float | None) -> None:
+    """float32 logits in place: times ``scale``, then (``cap`` given) cap * tanh(logits / cap)."""
+    _need_cuda(logits)
+    _contig("logits", logits)
+    assert logits.dtype == torch.float32
+    call("nhv_scale_softcap", logits.data_ptr(), float(scale), float(cap or 0.0), logits.numel(), stream_ptr())
 
 
 def sigmoid_mul(out, x, gate) -> None:
@@ -452,13 +561,17 @@ def moe_combine(out, y, x, ids, weights, slot_pos, n_experts: int, shared=None, 
 
 
 def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rotary_dim: int, nq: int, nkv: int, dk: int,
-                    dv: int, eps: float | None, bias=None, values_from_keys: bool = False) -> None:
+                    dv: int, eps: float | None, bias=None, values_from_keys: bool = False, q_weight=None,
+                    k_weight=None) -> None:
     """qkv [T, nq*dk + nkv*dk + nkv*dv] -> q_out [T, nq*dk] (rotated, then scaled to unit root mean square; eps None:
     no norm) and K / V rows in kv_pages [pages, 2, nkv, page_size, row] at slot_mapping.  kv_pages None: queries only.
     ``bias`` (one element per query and key column of qkv, in its type) is added in 32-bit before the rotation.
     ``values_from_keys``: the stored values are the key heads as projected (bias added, not rotated); qkv then ends
-    with the keys (it may have further columns that this op does not read) and dv == dk."""
-    _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, bias)
+    with the keys (it may have further columns that this op does not read) and dv == dk.  ``q_weight`` / ``k_weight``
+    [dk]: the normed query / key heads times this weight (one weight for all heads of a kind)."""
+    _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, bias, q_weight, k_weight)
+    for hw in (q_weight, k_weight):
+        assert hw is None or (hw.dtype == qkv.dtype and hw.is_contiguous() and hw.numel() == dk and eps is not None)
     assert bias is None or (bias.dtype == qkv.dtype and bias.is_contiguous() and bias.numel() == nq * dk + nkv * dk)
     assert qkv.stride(-1) == 1 and q_out.stride(-1) == 1 and qkv.dim() == 2 and q_out.dim() == 2
     n_tokens = qkv.shape[0]
@@ -475,44 +588,48 @@ def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rota
     call("nhv_rope_norm_store", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), q_out.data_ptr(), q_out.stride(0),
          _ptr(kv_pages), _ptr(slot_mapping), _ptr(positions), _ptr(cos_sin), int(rotary_dim),
          0 if cos_sin is None else cos_sin.shape[0], n_tokens, nq, nkv, dk, dv, row, page_size, n_pages,
-         -1.0 if eps is None else float(eps), _ptr(bias), int(bool(values_from_keys)), stream_ptr())
+         -1.0 if eps is None else float(eps), _ptr(bias), int(bool(values_from_keys)), _ptr(q_weight), _ptr(k_weight),
+         stream_ptr())
 
 
 def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_tokens: int, nq: int, nkv: int,
-                        dk: int, dv: int, scale: float, sinks=None, window: int = 0, chunk: int = 0) -> None:
+                        dk: int, dv: int, scale: float, sinks=None, window: int = 0, chunk: int = 0, slopes=None) -> None:
     """Causal attention of this step's tokens over the pages with key heads of dk and value heads of dv elements:
     q [T, nq*dk] -> out [T, nq*dv].  ``sinks`` [nq] float32: a term exp(sink) in each head's softmax denominator.
     ``window`` > 0: the last ``window`` keys only; ``chunk`` > 0: only the keys of the query's own chunk of ``chunk``
-    positions, counted from position 0 of the request."""
-    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks)
+    positions, counted from position 0 of the request.  ``slopes`` [nq] float32: head h's score loses slopes[h] times
+    the distance between query and key.  Pages with one plane ([pages, 1, nkv, page_size, row]): a row is the key and
+    its leading dv elements are the value."""
+    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks, slopes)
     _contig("kv_pages", kv_pages)
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and out.dtype == q.dtype == kv_pages.dtype
-    n_pages, two, h, page_size, row = kv_pages.shape
-    assert two == 2 and h == nkv and row >= max(dk, dv)
+    n_pages, planes, h, page_size, row = kv_pages.shape
+    assert planes in (1, 2) and h == nkv and row >= max(dk, dv) and (planes == 2 or dv <= dk)
     assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq)
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == nq)
     call("nhv_attention_simt_ex", dtype_code(q), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
          kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(),
          n_seqs, n_tokens, nq, nkv, dk, dv, row, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks),
-         stream_ptr())
+         _ptr(slopes), planes, stream_ptr())
 
 
 SINK_ATTENTION_ON_TENSOR_CORES = True     # tests switch it off to compare with the CUDA-core kernel at the same shapes
 
 
 def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, dv: int, scale: float, sinks=None,
-                   window: int = 0, chunk: int = 0) -> None:
+                   window: int = 0, chunk: int = 0, slopes=None) -> None:
     """Attention of the step's tokens over the cache for layers with a sink and / or value heads of another size
     than their key heads: picks the kernel for the dtype and sizes.  bfloat16 with key and value heads of one size
     (in steps of 16) runs on the tensor cores like ``attention``; float32 and unequal head sizes on the CUDA cores."""
     if (SINK_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and kv_pages.shape[-1] == dk
-            and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
+            and slopes is None and kv_pages.shape[1] == 2 and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
         attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
                               batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
                               nq, nkv, dk, scale, window, sinks, chunk)
         return
     attention_sink_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
-                        nq, nkv, dk, dv, scale, sinks, window, chunk)
+                        nq, nkv, dk, dv, scale, sinks, window, chunk, slopes)
 
 
 def linear_f32(out, x, weight) -> None:

@@ -1,10 +1,10 @@
-from . import (attention, block, delta_rule, embedding, feed_forward, mlstm, moe, norm, parallel_mixer, position,  # noqa: F401
-               sink_attention, state_space)    # (importing registers the built-in parts)
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block, BuildEnv, CacheView, CompositeNeed,
+from . import (attention, block, delta_rule, embedding, feed_forward, input_filter, latent_attention, mlstm, moe, norm,  # noqa: F401
+               parallel_mixer, position, sink_attention, state_space)    # (importing registers the built-in parts)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, FILTERS, HEADS, MIXERS, NORMS, POSITIONS, Block, InputFilter, SharedPagesNeed, BuildEnv, CacheView, CompositeNeed,
                    Embedding,
                    FeedForward, FixedStateNeed, Head, Mixer, Norm, PagedKVNeed, Part, Pending, PositionEncoding)
 from .spec import LayerRun, LayerSpec, ModelSpec, ParamDecl, PartSpec, PartUse, Source, part
 
-__all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "Block", "BuildEnv", "CacheView", "CompositeNeed",
+__all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "FILTERS", "InputFilter", "SharedPagesNeed", "HEADS", "MIXERS", "NORMS", "POSITIONS", "Block", "BuildEnv", "CacheView", "CompositeNeed",
            "Embedding", "FeedForward", "FixedStateNeed", "Head", "Mixer", "Norm", "PagedKVNeed", "Part", "Pending", "PositionEncoding",
            "LayerRun", "LayerSpec", "ModelSpec", "ParamDecl", "PartSpec", "PartUse", "Source", "part"]

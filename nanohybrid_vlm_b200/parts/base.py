@@ -6,7 +6,7 @@ dtype, device); it declares its tensors (:class:`~.spec.ParamDecl`), receives th
 ``bind`` and then computes on device tensors.  No part knows which model it is in.
 
 Adding a part: subclass the interface, then ``MIXERS.register("name", Class)`` (or
-``FEED_FORWARDS``, ``NORMS``, ``POSITIONS``, ``BLOCKS``, ``EMBEDDINGS``, ``HEADS``).  A model
+``FEED_FORWARDS``, ``NORMS``, ``POSITIONS``, ``FILTERS``, ``BLOCKS``, ``EMBEDDINGS``, ``HEADS``).  A model
 description refers to it as ``part("name", ...)``.
 """
 from __future__ import annotations
@@ -47,6 +47,7 @@ MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
+FILTERS = Registry("input filter")
 BLOCKS = Registry("block arrangement")
 
 
@@ -54,12 +55,14 @@ BLOCKS = Registry("block arrangement")
 class PagedKVNeed:
     """Keys and values of every token (or of the last ``window`` tokens, or of the current chunk of ``chunk``
     positions) in pages.  ``v_head_dim``: the size of a value head where it differs from a key head's; a page row then
-    has room for the larger of the two and each kind uses its leading elements."""
+    has room for the larger of the two and each kind uses its leading elements.  ``planes``: 2 for a key and a value
+    plane per page; 1 for pages that hold one row per token and head (a latent vector that is key and value at once)."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
     chunk: int | None = None
+    planes: int = 2
 
     @property
     def row_dim(self) -> int:
@@ -74,10 +77,35 @@ class FixedStateNeed:
 
 
 @dataclass(frozen=True)
+class SharedPagesNeed:
+    """The place of a paged need in a run that reads another run's pages (``LayerRun.cache_from``) instead of keeping
+    its own: nothing is allocated for it, and the run's view shows the other run's pages, not to be written."""
+
+
+@dataclass(frozen=True)
 class CompositeNeed:
     """Several things kept by one mixer (a mixer made of mixers, or one with pages and a state): the run's
     :class:`CacheView` then has one child view per entry, in this order."""
     parts: tuple
+
+
+def need_leaves(need) -> list:
+    """The paged / fixed-state / shared needs that a need is made of (a composite's entries, flattened in order)."""
+    if need is None:
+        return []
+    if isinstance(need, CompositeNeed):
+        return [leaf for sub in need.parts for leaf in need_leaves(sub)]
+    return [need]
+
+
+def with_shared_pages(need):
+    """The same need with every paged entry replaced by :class:`SharedPagesNeed`; what else a run keeps (fixed-size
+    state of its mixer or of its block) stays its own."""
+    if isinstance(need, CompositeNeed):
+        return CompositeNeed(tuple(with_shared_pages(sub) for sub in need.parts))
+    if isinstance(need, PagedKVNeed):
+        return SharedPagesNeed()
+    return need
 
 
 class BuildEnv:
@@ -190,6 +218,18 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class InputFilter(Part):
+    """Something a sub-block's input passes on its way from the norm (a short filter over time, for instance).
+    ``state_need()``: what it keeps per request between steps (a :class:`FixedStateNeed`) or None.  Filters of one
+    block that read the same input may share one state; the block that arranges them decides."""
+
+    def state_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, batch, state) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
     """How positions enter the model.  ``rotary()`` gives (table [max_position, rotary_dim] fp32 with
     cos then sin halves, rotary_dim) for mixers that rotate queries and keys, or None;
@@ -240,6 +280,12 @@ class Block:
     @property
     def cache_owner(self) -> Mixer | None:
         return self.parts.get("mixer")
+
+    def cache_need(self):
+        """What a run of this layer keeps between steps: by default what its ``cache_owner`` needs.  A block that
+        keeps something itself returns a :class:`CompositeNeed` and hands each part its child view."""
+        owner = self.cache_owner
+        return owner.cache_need() if owner is not None else None
 
     def forward(self, hidden, residual, batch, cache: CacheView):
         raise NotImplementedError

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Pending
+from .base import BLOCKS, FEED_FORWARDS, FILTERS, MIXERS, NORMS, Block, CompositeNeed, Pending
 
 
 class PreNormResidualBlock(Block):
@@ -28,23 +28,51 @@ class ParallelResidualBlock(Block):
     """One norm whose output both the mixer and the feed-forward read: x <- x + mult * (mixer(h) + ffn(h)) with
     h = norm(x).  The residual stream x is kept in float32: the block hands on its sub-blocks' outputs as a
     :class:`Pending` (each with its factor) and the next norm (the next layer's, or the model's last) adds them in
-    32-bit.  Parameter: ``residual_mult``.  A layer may have no feed-forward."""
-    SLOTS = {"mixer": MIXERS, "norm": NORMS, "ffn": FEED_FORWARDS}
-    OPTIONAL = ("ffn",)
+    32-bit.  Parameter: ``residual_mult``.  A layer may have no feed-forward.
+
+    Optional input filters (``mixer_filter``, ``ffn_filter``; registry FILTERS): what each sub-block reads is then the
+    filter's output over h.  Both filters read the same h, so the block keeps ONE state for them (the filter's
+    ``state_need``) beside what the mixer keeps: the layer's need is the composite (filter state, mixer's need), and
+    the mixer gets its child view."""
+    SLOTS = {"mixer": MIXERS, "norm": NORMS, "ffn": FEED_FORWARDS, "mixer_filter": FILTERS, "ffn_filter": FILTERS}
+    OPTIONAL = ("ffn", "mixer_filter", "ffn_filter")
 
     def __init__(self, spec, parts):
         super().__init__(spec, parts)
         self.mult = float(spec.get("residual_mult", 1.0))
+        self.filters = [parts.get("mixer_filter"), parts.get("ffn_filter") if "ffn" in parts else None]
+        if "ffn_filter" in parts and "ffn" not in parts:
+            raise ValueError("a filter in front of the feed-forward needs a feed-forward")
+        both = [f for f in self.filters if f is not None]
+        if len(both) == 2 and both[0].state_need() != both[1].state_need():
+            raise ValueError("the two input filters of a block share one state: their sizes must agree")
+        self.filtered = bool(both)
+
+    def cache_need(self):
+        need = super().cache_need()
+        if not self.filtered:
+            return need
+        return CompositeNeed((next(f for f in self.filters if f is not None).state_need(), need))
 
     def forward(self, hidden, residual, batch, cache):
         if residual is None:
             residual = hidden if hidden.dtype == torch.float32 else hidden.float()
             hidden = Pending()
         x = self.norm.forward_add(hidden, residual)
-        terms = [(t, self.mult * c) for t, c in self.mixer.forward_terms(x, batch, cache)]
+        xm = xf = x
+        if self.filtered:
+            kept, cache = cache.children
+            fm, ff = self.filters
+            if fm is not None and ff is not None:
+                xm, xf = fm.forward_pair(ff, x, batch, kept.state)
+            elif fm is not None:
+                xm = fm.forward(x, batch, kept.state)
+            else:
+                xf = ff.forward(x, batch, kept.state)
+        terms = [(t, self.mult * c) for t, c in self.mixer.forward_terms(xm, batch, cache)]
         ffn = self.parts.get("ffn")
         if ffn is not None:
-            terms.append((ffn.forward(x, batch), self.mult))
+            terms.append((ffn.forward(xf, batch), self.mult))
         return Pending(tuple(terms)), residual
 
 

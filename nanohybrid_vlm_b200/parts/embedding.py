@@ -9,7 +9,8 @@ rows in the model's dtype; "float32": rows in 32-bit, for blocks that keep their
 rows pass before they become the stream, its tensors under the same prefix; the stream is then float32).  Head
 parameters: ``vocab_size``, ``tied``, ``exact`` (True: the 32-bit sums of the product are the logits; False: rounded to
 the model's dtype first and then widened, as the reference's head does), ``source`` (the checkpoint's name of an untied
-head's table; the part's own tensor then carries that name instead of "weight").
+head's table; the part's own tensor then carries that name instead of "weight"), ``scale`` (a factor on the logits),
+``softcap`` (c: the scaled logits become c * tanh(logits / c); both in 32-bit, on the rows that are asked for).
 """
 from __future__ import annotations
 
@@ -70,6 +71,10 @@ class LMHead(Head):
         self.tied = bool(spec.get("tied", False))
         self.exact = bool(spec.get("exact", False))
         self.source = spec.get("source")
+        self.scale = float(spec.get("scale") or 1.0)
+        self.softcap = spec.get("softcap")
+        if self.softcap is not None and float(self.softcap) <= 0:
+            raise ValueError("a soft cap on the logits must be positive")
 
     def params(self):
         if self.tied:
@@ -91,8 +96,10 @@ class LMHead(Head):
         logits = self.new(rows_hidden.shape[0], self.vocab, dtype=torch.float32)
         if self.exact:
             ops.linear_f32(logits, rows_hidden, self.w_weight)
-            return logits
-        ops.linear(logits, rows_hidden, self.w_weight)
+        else:
+            ops.linear(logits, rows_hidden, self.w_weight)
+        if self.scale != 1.0 or self.softcap is not None:
+            ops.scale_softcap(logits, self.scale, self.softcap)
         return logits
 
 

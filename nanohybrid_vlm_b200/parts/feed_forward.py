@@ -74,5 +74,38 @@ class GatedMLP(FeedForward):
         return y
 
 
+class DenseMLP(FeedForward):
+    """down(act(up(x))): a feed-forward without a gate.  Parameters: ``intermediate_size``, ``activation`` ("relu2": the
+    square of relu), ``names`` (the checkpoint's names of the two matrices; default ("up", "down")).  Tensors: ``up``
+    [I, width], ``down`` [width, I]."""
+    ACTIVATIONS = {"relu2": "relu_squared"}
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.inter = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "relu2")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {self.activation!r}; known: {sorted(self.ACTIVATIONS)}")
+        self.names = tuple(spec.get("names", ("up", "down")))
+
+    def params(self):
+        H, I = self.env.hidden_size, self.inter
+        up, down = self.names
+        return [ParamDecl("up", (I, H), sources=(Source(up, 0, I),)), ParamDecl("down", (H, I), sources=(Source(down, 0, H),))]
+
+    def streamed_weights(self):
+        return [(self.w_up, 0), (self.w_down, 0)]
+
+    def forward(self, x, batch):
+        T = x.shape[0]
+        act = self.new(T, self.inter)
+        ops.linear(act, x, self.w_up)
+        getattr(ops, self.ACTIVATIONS[self.activation])(act)
+        y = self.new(T, self.env.hidden_size)
+        ops.linear(y, act, self.w_down)
+        return y
+
+
+FEED_FORWARDS.register("dense_mlp", DenseMLP)
 FEED_FORWARDS.register("swiglu", SwiGLU)
 FEED_FORWARDS.register("gated_mlp", GatedMLP)

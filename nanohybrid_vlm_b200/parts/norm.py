@@ -1,7 +1,9 @@
 """Norms: RMSNorm with the residual add fused in (nanovllm/layers/layernorm.py:5-50), and Dynamic Tanh.
 
 Parameters: ``width``, ``eps``, ``weight_offset`` (0 for ``x * w``; 1 for the ``x * (1 + w)``
-convention some models store), ``source`` (the checkpoint's name of the weight, default "weight").
+convention some models store), ``source`` (the checkpoint's name of the weight, default "weight"), ``groups`` (the
+row is cut into this many equal consecutive parts and each is divided by the root mean square of its own elements;
+default 1; over a float32 stream only).
 
 Over a residual stream kept in float32 (``forward_add`` / ``forward_add_rows`` given a :class:`Pending`) the terms
 are added in 32-bit, the statistics and the product with the weight are 32-bit, and the result is rounded once.
@@ -22,12 +24,20 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight_offset = float(spec.get("weight_offset", 0.0))
         self.source = spec.get("source", "weight")
+        self.groups = int(spec.get("groups", 1))
+        if self.groups < 1 or self.width % self.groups:
+            raise ValueError(f"a norm over {self.width} elements does not divide into {self.groups} parts")
+
+    def _plain_only(self):
+        if self.groups != 1:
+            raise TypeError("a norm in groups works over a float32 residual stream: it takes a Pending")
 
     def params(self):
         return [ParamDecl("weight", (self.width,), init="norm" if self.weight_offset == 0.0 else "zeros_noise",
                           sources=(Source(self.source, 0, self.width),))]
 
     def forward(self, x):
+        self._plain_only()
         out = self.new(*x.shape)
         ops.rmsnorm(out, x, self.w_weight, self.eps, weight_offset=self.weight_offset)
         return out
@@ -36,8 +46,10 @@ class RMSNorm(Norm):
         if isinstance(x, Pending):
             x = x.settled()
             out = self.new(*residual.shape)
-            ops.rmsnorm_stream(out, residual, self.w_weight, self.eps, addends=x.terms, weight_offset=self.weight_offset)
+            ops.rmsnorm_stream(out, residual, self.w_weight, self.eps, addends=x.terms, weight_offset=self.weight_offset,
+                               groups=self.groups)
             return out
+        self._plain_only()
         out = self.new(*x.shape)
         ops.rmsnorm(out, x, self.w_weight, self.eps, residual=residual, weight_offset=self.weight_offset)
         return out
@@ -47,8 +59,9 @@ class RMSNorm(Norm):
             x = x.settled()
             out = self.new(rows.numel(), residual.shape[-1])
             ops.rmsnorm_stream(out, residual, self.w_weight, self.eps, addends=x.terms, rows=rows, write_stream=False,
-                               weight_offset=self.weight_offset)
+                               weight_offset=self.weight_offset, groups=self.groups)
             return out
+        self._plain_only()
         out = self.new(rows.numel(), x.shape[-1])
         ops.rmsnorm(out, x, self.w_weight, self.eps, residual=residual, rows=rows, write_residual=False,
                     weight_offset=self.weight_offset)

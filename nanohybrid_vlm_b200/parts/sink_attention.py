@@ -11,7 +11,13 @@ last n), ``chunk`` (None, or n: a query sees only the keys of its own chunk of n
 position 0 of the request), ``values`` ("projected": a projection of their own; "keys": the values are the key heads as
 projected, bias included, before the rotation, and there is no value projection), ``bias`` (True: q, k and the output
 projection have biases ``q.b``, ``k.b``, ``o.b``), ``output_gate`` (None, or "sigmoid": the concatenated heads are
-multiplied by sigmoid(g(x)) before the output projection, g a projection of the mixer's input).
+multiplied by sigmoid(g(x)) before the output projection, g a projection of the mixer's input; "sigmoid_head": g has one
+output per head and head h is multiplied by sigmoid(g(x))_h), ``qk_norm_weight`` (True: after the unit norm each
+q and k head is multiplied by a learned weight [head_dim], ``q.norm`` / ``k.norm``, shared by the heads),
+``distance_slope_base`` (None, or b: the score of head h at distance n behind the query loses 2^(-b (h + 1) / H) * n),
+``own_kv`` (False: the layer has no key / value projections, norms or pages of its own and reads the keys and values
+that another run stored, ``LayerRun.cache_from``), ``keep_window`` (how many keys the pages keep, where that is more
+than this layer's own ``window`` shows: a layer whose pages another layer with a wider window reads; None: all).
 
 Tensors: ``qkv`` [(nq + nkv) d (+ nkv dv) (+ nq dv), width], rows q then k then v then g, packed from the
 checkpoint's ``q``, ``k``, ``v``, ``g`` (those that exist); ``qk_bias`` [(nq + nkv) d] from ``q.b``, ``k.b``; ``sink``
@@ -39,6 +45,9 @@ class SinkAttention(Mixer):
         self.eps = None if eps is None else float(eps)
         self.has_sink = bool(spec.get("sink", True))
         self.window = spec.get("window")
+        self.keep_window = spec.get("keep_window", self.window)
+        if self.keep_window is not None and (self.window is None or self.keep_window < self.window):
+            raise ValueError("the pages must keep at least the keys that the layer's window shows")
         self.chunk = spec.get("chunk")
         self.values = spec.get("values", "projected")
         if self.values not in ("projected", "keys"):
@@ -47,16 +56,29 @@ class SinkAttention(Mixer):
             raise ValueError(f"values that are the keys have the keys' size {self.d}, not {self.dv}")
         self.bias = bool(spec.get("bias", False))
         self.gate = spec.get("output_gate")
-        if self.gate not in (None, "sigmoid"):
-            raise ValueError(f"an output gate is None or 'sigmoid', not {self.gate!r}")
+        if self.gate not in (None, "sigmoid", "sigmoid_head"):
+            raise ValueError(f"an output gate is None, 'sigmoid' or 'sigmoid_head', not {self.gate!r}")
         self.position = env.position(spec.get("position"))
-        self.q_size, self.k_size = self.nq * self.d, self.nkv * self.d
-        self.v_size = self.nkv * self.dv if self.values == "projected" else 0
-        self.g_size = self.nq * self.dv if self.gate else 0
+        self.own_kv = bool(spec.get("own_kv", True))
+        self.norm_weight = bool(spec.get("qk_norm_weight", False))
+        if self.norm_weight and self.eps is None:
+            raise ValueError("a weight on the q/k norm needs the norm (unit_norm_eps)")
+        base = spec.get("distance_slope_base")
+        self.slopes = None
+        if base is not None:
+            import torch
+            self.slopes = torch.tensor([2.0 ** (-float(base) * (h + 1) / self.nq) for h in range(self.nq)],
+                                       dtype=torch.float32, device=env.device)
+        self.q_size = self.nq * self.d
+        self.k_size = self.nkv * self.d if self.own_kv else 0
+        self.v_size = self.nkv * self.dv if self.values == "projected" and self.own_kv else 0
+        self.g_size = (self.nq if self.gate == "sigmoid_head" else self.nq * self.dv) if self.gate else 0
 
     def params(self):
         H = self.env.hidden_size
-        sources = [Source("q", 0, self.q_size), Source("k", self.q_size, self.k_size)]
+        sources = [Source("q", 0, self.q_size)]
+        if self.k_size:
+            sources.append(Source("k", self.q_size, self.k_size))
         if self.v_size:
             sources.append(Source("v", self.q_size + self.k_size, self.v_size))
         if self.g_size:
@@ -67,14 +89,20 @@ class SinkAttention(Mixer):
         ]
         if self.has_sink:
             decls.append(ParamDecl("sink", (self.nq,), storage="float32"))
+        if self.norm_weight:
+            decls.append(ParamDecl("q.norm", (self.d,), init="norm"))
+            if self.own_kv:
+                decls.append(ParamDecl("k.norm", (self.d,), init="norm"))
         if self.bias:
+            if not self.own_kv:
+                raise ValueError("projection biases are not offered for a layer without keys of its own")
             decls += [ParamDecl("qk_bias", (self.q_size + self.k_size,), init="zeros_noise",
                                 sources=(Source("q.b", 0, self.q_size), Source("k.b", self.q_size, self.k_size))),
                       ParamDecl("o.b", (H,), init="zeros_noise")]
         return decls
 
     def cache_need(self):
-        return PagedKVNeed(self.nkv, self.d, self.window, v_head_dim=self.dv, chunk=self.chunk)
+        return PagedKVNeed(self.nkv, self.d, self.keep_window, v_head_dim=self.dv, chunk=self.chunk)
 
     def streamed_weights(self):
         return [(self.w_qkv, 0), (self.w_o, 0)]
@@ -86,13 +114,19 @@ class SinkAttention(Mixer):
         rot = self.position.rotary() if self.position is not None else None
         table, rotary_dim = rot if rot is not None else (None, 0)
         q = self.new(T, self.q_size)
+        if cache.writes != self.own_kv:
+            raise ValueError("a layer with keys of its own writes its pages; one without reads another run's (cache_from)")
         ops.rope_norm_store(qkv, q, cache.pages if cache.writes else None, cache.tables.slot_mapping, batch.positions,
                             table, rotary_dim, self.nq, self.nkv, self.d, self.dv, self.eps,
-                            bias=self.w_qk_bias if self.bias else None, values_from_keys=self.values == "keys")
+                            bias=self.w_qk_bias if self.bias else None, values_from_keys=self.values == "keys",
+                            q_weight=self.w_q_norm if self.norm_weight else None,
+                            k_weight=self.w_k_norm if self.norm_weight and self.own_kv else None)
         o = self.new(T, self.nq * self.dv)
         ops.attention_sink(o, q, cache.pages, cache.tables, batch, self.nq, self.nkv, self.d, self.dv, self.scale,
-                           self.w_sink if self.has_sink else None, self.window or 0, self.chunk or 0)
-        if self.gate:
+                           self.w_sink if self.has_sink else None, self.window or 0, self.chunk or 0, self.slopes)
+        if self.gate == "sigmoid_head":
+            ops.sigmoid_mul_heads(o, o, qkv[:, self.q_size + self.k_size + self.v_size:], self.dv)
+        elif self.gate:
             ops.sigmoid_mul(o, o, qkv[:, self.q_size + self.k_size + self.v_size:])
         y = self.new(T, self.env.hidden_size)
         ops.linear(y, o, self.w_o)

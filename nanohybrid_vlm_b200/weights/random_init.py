@@ -38,6 +38,8 @@ INITS = {
     "zeros_noise": _normal(0.01),
     "dyntanh_alpha": _normal(0.05, 0.5),        # the scalar of a Dynamic Tanh norm
     "gate_bias": _normal(1.0),                  # biases of recurrent gates: spread, so that decays differ
+    "filter_taps": _normal(0.3),                # short filters over time: large enough to show in the output
+    "unit": _normal(1.0),                       # small inner matrices whose input is bounded (a tanh)
     "zeros": lambda shape, gen, device: torch.zeros(shape, dtype=torch.float32, device=device),
 }
 
