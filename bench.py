@@ -5,6 +5,7 @@
     python bench.py --breakdown              where a decode step's and a prefill's time goes, by kind of kernel
     python bench.py --designs                Muvonex beside a Qwen3 of equal size (prefill, decode, time by kind of kernel)
     python bench.py --designs nomudra        Nomudra beside a Muvonex of equal active size, the same way
+    python bench.py --designs ginodra        Ginodra beside a Muvonex of equal size, the same way
 
 The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 layers, width 4096,
 32/8 heads of 128, feed-forward 12288, vocabulary 151936), bfloat16, random weights, batch 8,
@@ -679,6 +680,28 @@ def nomudra_config(width: int, heads: int, ff: int, layers: int) -> dict:
                 layers=[attention if i % 2 == 0 else mlstm for i in range(layers)], dtype="bfloat16")
 
 
+def ginodra_config(width: int, heads: int, ff: int, layers: int) -> dict:
+    """Attention over latents (heads of 128 + 64 rotated, a latent of 512, queries through a latent of 3/8 of the width),
+    attention in a window of 1,024 over a quarter as many key heads, the generalised delta rule with heads of 64, and a
+    second windowed layer that reads the first one's keys, in turn; every layer with the squared-ReLU feed-forward of two
+    matrices, as wide as holds the weights of the other designs' three (``ff`` * 3 / 2), and three filter taps."""
+    dense = dict(kind="dense", ff=ff * 3 // 2)
+    latent = dict(type="latent_attention", mlp=dense, mixer=dict(
+        heads=heads, dim=128, rot_dim=64, vdim=128, q_rank=width * 3 // 8, kv_rank=512, scale=192 ** -0.5,
+        rot=dict(base=10000.0, dims=64)))
+    window = dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024))
+    delta = dict(type="general_delta", mlp=dense, mixer=dict(heads=width // 64, dim=64, decay_rank=64))
+    kinds = [latent, dict(type="attention", mlp=dense, mixer=window), delta, None]
+    out = []
+    for i in range(layers):
+        layer = kinds[i % 4]
+        if layer is None:       # the windowed layer before it in this group of four owns the keys
+            layer = dict(type="attention", mlp=dense, mixer=dict(window, kv_from=i - 2))
+        out.append(layer)
+    return dict(architecture="Ginodra", vocab=DESIGN_VOCAB, width=width, norm=dict(eps=1e-6, groups=4), residual_mult=1.0,
+                canon=dict(taps=3), logit_scale=1.0, logit_softcap=30.0, layers=out, dtype="bfloat16")
+
+
 def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weights: float) -> dict:
     """A Qwen3 of this width whose layers hold as many weights as ``layer_weights`` (the feed-forward takes up the
     difference, rounded to 256)."""
@@ -691,7 +714,8 @@ def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weight
 
 def bench_designs(args) -> dict:
     """Prefill and decode throughput of Muvonex beside a Qwen3 of equal size (``--designs``), or of Nomudra beside a
-    Muvonex whose layers hold as many weights as a Nomudra token uses (``--designs nomudra``), and the time of each kind
+    Muvonex whose layers hold as many weights as a Nomudra token uses (``--designs nomudra``), or of Ginodra beside a
+    Muvonex of equal size (``--designs ginodra``), and the time of each kind
     of kernel in a prefill step (CUDA events around every launch of an eager run) with its share of the measured
     roofline."""
     import torch
@@ -710,7 +734,10 @@ def bench_designs(args) -> dict:
              "delta_rule": "delta_rule", "ssd_scan": "ssd_scan", "gated_rmsnorm": "gated_norm", "sample": "sample",
              "dyntanh": "norm", "dyntanh_stream": "norm", "embed_dyntanh": "embed", "mlstm_scan": "mlstm_scan",
              "sigmoid_mul": "act_mul", "add_row_bias": "act_mul", "clamped_glu": "act_mul", "moe_route": "router",
-             "moe_experts": "experts", "moe_combine": "experts_sum"}
+             "moe_experts": "experts", "moe_combine": "experts_sum", "causal_filter_add": "short_conv",
+             "latent_rope_store": "rope_store", "linear_heads": "gemm_heads", "attention_sink_simt": "attention",
+             "latent_attention": "attention", "general_delta": "delta_rule", "sigmoid_mul_heads": "act_mul",
+             "relu_squared": "act_mul", "scale_softcap": "act_mul"}
     kinds = {k: v for k, v in kinds.items() if hasattr(ops, k)}
     stock = {name: getattr(ops, name) for name in kinds}
     gen = torch.Generator().manual_seed(SEED)
@@ -847,6 +874,14 @@ def bench_designs(args) -> dict:
             ff = max(256, int(round((sz["ff"] + (per_layer - m0 / layers) / (3 * sz["width"])) / 256)) * 256)
             results[name] = {"nomudra": n, "muvonex": run_one(muvonex_config(sz["width"], sz["heads"], ff, layers), DESIGN_VOCAB)}
             continue
+        if args.designs == "ginodra":
+            g = run_one(ginodra_config(sz["width"], sz["heads"], sz["ff"], layers), DESIGN_VOCAB)
+            # a Muvonex whose dense feed-forward makes up for the difference in the mixers' weights
+            per_layer = (g["weights_m"] * 1e6 - DESIGN_VOCAB * sz["width"]) / layers
+            m0 = run_one_weights(muvonex_config(sz["width"], sz["heads"], sz["ff"], layers))
+            ff = max(256, int(round((sz["ff"] + (per_layer - m0 / layers) / (3 * sz["width"])) / 256)) * 256)
+            results[name] = {"ginodra": g, "muvonex": run_one(muvonex_config(sz["width"], sz["heads"], ff, layers), DESIGN_VOCAB)}
+            continue
         mcfg = muvonex_config(sz["width"], sz["heads"], sz["ff"], layers)
         m = run_one(mcfg, DESIGN_VOCAB)
         layer_weights = (m["weights_m"] * 1e6 - DESIGN_VOCAB * sz["width"]) / layers
@@ -878,7 +913,7 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
     ap.add_argument("--breakdown", action="store_true",
                     help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
-    ap.add_argument("--designs", nargs="?", const="muvonex", default=None, choices=["muvonex", "nomudra"],
+    ap.add_argument("--designs", nargs="?", const="muvonex", default=None, choices=["muvonex", "nomudra", "ginodra"],
                     help="two designs side by side, prefill and decode throughput at a few layer sizes, one JSON line: "
                          "Muvonex beside a Qwen3 of equal size (the default), or Nomudra beside a Muvonex of equal active size")
     ap.add_argument("--design-size", default="all", choices=["all", *DESIGN_SIZES], help="one size of --designs")

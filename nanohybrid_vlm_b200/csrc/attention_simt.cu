@@ -31,12 +31,11 @@
 
 constexpr int AT_WARPS = 4;
 constexpr int AT_CHUNK = 32;
-constexpr int AT_MAX_PAIRS = 32;
-constexpr int AT_PAIRS_PER_WARP = AT_MAX_PAIRS / AT_WARPS;  // 8
-constexpr int AT_MAX_D = 256;
-constexpr int AT_COLS = AT_MAX_D / 32;  // output columns per lane
+constexpr int AT_MAX_D = 2048;
+constexpr int AT_ACC = 64;              // output accumulators per lane: (pairs per warp) x (columns per lane)
 
-template <typename T>
+// COLS: output columns per lane (value heads of up to 32 COLS elements); a warp then carries AT_ACC / COLS pairs.
+template <typename T, int COLS>
 __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                                        const T* __restrict__ kv_pages, const int* __restrict__ block_table,
                                        int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
@@ -44,6 +43,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
                                        float scale, int TQ, int GS, int dv, int row, const float* __restrict__ sinks,
                                        int chunk, const float* __restrict__ slopes, int planes) {
   extern __shared__ float smem[];
+  constexpr int AT_COLS = COLS, AT_PAIRS_PER_WARP = AT_ACC / COLS, AT_MAX_PAIRS = AT_PAIRS_PER_WARP * AT_WARPS;
   pdl_prologue();
   const int G = nq / nkv;
   const int kvh = blockIdx.y;
@@ -69,8 +69,10 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
 
   const int ks = d + 1;                        // padded key row: lane <-> key reads hit 32 banks
   float* Ks = smem;                            // [32][d+1]
-  float* Vs = Ks + AT_CHUNK * ks;              // [32][dv]
-  float* Qs = Vs + AT_CHUNK * dv;              // [pairs][d]
+  // one plane: the values are the keys' leading elements, read where the keys lie
+  float* Vs = planes == 2 ? Ks + AT_CHUNK * ks : Ks;            // [32][dv]
+  const int vs = planes == 2 ? dv : ks;
+  float* Qs = Ks + AT_CHUNK * ks + (planes == 2 ? AT_CHUNK * dv : 0);      // [pairs][d]
   float* Ps = Qs + AT_MAX_PAIRS * d;           // [warps][32]
   __shared__ int key_ok[AT_CHUNK];
 
@@ -127,7 +129,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
         if (c < dv) vx = planes == 2 ? to_f32<T>(kv_pages[base + (size_t)nkv * page_size * row]) : (c < d ? kx : 0.f);
       }
       if (c < d) Ks[r * ks + c] = kx;
-      if (c < dv) Vs[r * dv + c] = vx;
+      if (planes == 2 && c < dv) Vs[r * dv + c] = vx;
     }
     __syncthreads();
 
@@ -163,7 +165,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
         const int c = lane + cc * 32;
         if (c < dv) {
           float acc = 0.f;
-          for (int r = 0; r < AT_CHUNK; ++r) acc = fmaf(Ps[warp * AT_CHUNK + r], Vs[r * dv + c], acc);
+          for (int r = 0; r < AT_CHUNK; ++r) acc = fmaf(Ps[warp * AT_CHUNK + r], Vs[r * vs + c], acc);
           o[i][cc] = o[i][cc] * alpha + acc;
         }
       }
@@ -202,24 +204,35 @@ NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* 
   NHV_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
   NHV_REQUIRE(planes == 2 || (planes == 1 && dv <= d), "attention: pages have a key and a value plane, or one plane whose rows' leading elements are the values");
   const int G = nq / nkv;
-  const int GS = G < 8 ? G : 8;
-  const int TQ = AT_MAX_PAIRS / GS;
+  const int cols = dv <= 256 ? 8 : dv <= 512 ? 16 : dv <= 1024 ? 32 : 64;
+  const int max_pairs = AT_ACC / cols * AT_WARPS;
+  const int GS = G < 8 ? (G < max_pairs ? G : max_pairs) : (8 < max_pairs ? 8 : max_pairs);
+  const int TQ = max_pairs / GS;
   const int max_tiles = n_tokens / TQ + n_seqs;
-  const size_t smem = ((size_t)AT_CHUNK * (d + 1) + (size_t)AT_CHUNK * dv + (size_t)AT_MAX_PAIRS * d +
+  const size_t smem = ((size_t)AT_CHUNK * (d + 1) + (planes == 2 ? (size_t)AT_CHUNK * dv : 0) + (size_t)max_pairs * d +
                        AT_WARPS * AT_CHUNK) * sizeof(float);
+  NHV_REQUIRE(smem <= 227 * 1024, "attention: head sizes %d / %d need %zu bytes of shared memory", d, dv, smem);
   dim3 grid(max_tiles, nkv, (G + GS - 1) / GS);
-#define LAUNCH(T)                                                                                              \
-  do {                                                                                                         \
-    if (smem > 48 * 1024)                                                                                      \
-      NHV_CUDA(cudaFuncSetAttribute(attn_paged_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
-                                    (int)smem), "attention");                                                  \
-    nhv_launch(attn_paged_simt_kernel<T>, grid, AT_WARPS * 32, smem, stream,                                   \
-        (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,  \
-        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk, slopes, planes);      \
+#define LAUNCH(T, COLS)                                                                                              \
+  do {                                                                                                               \
+    if (smem > 48 * 1024)                                                                                            \
+      NHV_CUDA(cudaFuncSetAttribute(attn_paged_simt_kernel<T, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                    (int)smem), "attention");                                                        \
+    nhv_launch(attn_paged_simt_kernel<T, COLS>, grid, AT_WARPS * 32, smem, stream,                                   \
+        (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,        \
+        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk, slopes, planes);       \
   } while (0)
-  if (dtype == NHV_F32) LAUNCH(float);
-  else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
+#define LAUNCH_COLS(T)                 \
+  do {                                 \
+    if (cols == 8) LAUNCH(T, 8);       \
+    else if (cols == 16) LAUNCH(T, 16); \
+    else if (cols == 32) LAUNCH(T, 32); \
+    else LAUNCH(T, 64);                \
+  } while (0)
+  if (dtype == NHV_F32) LAUNCH_COLS(float);
+  else if (dtype == NHV_BF16) LAUNCH_COLS(__nv_bfloat16);
   else NHV_REQUIRE(false, "attention: unknown dtype %d", dtype);
+#undef LAUNCH_COLS
 #undef LAUNCH
   NHV_CHECK_LAUNCH("attention");
   return 0;

@@ -26,7 +26,7 @@
 
 constexpr int GD_WARPS = 4;
 constexpr int GD_MAX_D = 256;
-constexpr int GD_MAX_RANK = 128;
+constexpr int GD_MAX_RANK = 1024;
 constexpr int GD_CHUNK = 16;
 constexpr int GD_LANES = 8;
 constexpr int GD_THREADS = 128;

@@ -135,7 +135,7 @@ struct RowState {
 template <int NT>
 __device__ __forceinline__ void warp_tile(RowState& st, const uint32_t (&qf)[KS][4], const bf16* ks, const bf16* vs,
                                           int kb, int key_base, const int (&row_lo)[2], const int (&row_hi)[2],
-                                          float scale_log2) {
+                                          float scale_log2, const float (&row_slope)[2]) {
   const int lane = threadIdx.x & 31;
   float s[NT][4];
 #pragma unroll
@@ -159,7 +159,9 @@ __device__ __forceinline__ void warp_tile(RowState& st, const uint32_t (&qf)[KS]
     for (int e = 0; e < 4; ++e) {
       const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
       const int i = e >> 1;
-      const float v = (key >= row_lo[i] && key <= row_hi[i]) ? s[j][e] * scale_log2 : -INFINITY;
+      // row_slope: what the score loses per position of distance behind the query (0: nothing; the sum is then exact)
+      const float v = (key >= row_lo[i] && key <= row_hi[i])
+                          ? fmaf(-row_slope[i], (float)(row_hi[i] - key), s[j][e] * scale_log2) : -INFINITY;
       s[j][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -238,7 +240,7 @@ struct PrefillState {
 template <int MTW>
 __device__ __forceinline__ void warp_tile_prefill(PrefillState<MTW>& st, const bf16* qs, int qrow0, const bf16* ks, const bf16* vs,
                                                   int key_base, const int (&row_lo)[MTW][2], const int (&row_hi)[MTW][2],
-                                                  int w_lo, int w_hi, float scale_log2) {
+                                                  int w_lo, int w_hi, float scale_log2, const float (&row_slope)[MTW][2]) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -276,7 +278,8 @@ __device__ __forceinline__ void warp_tile_prefill(PrefillState<MTW>& st, const b
         for (int e = 0; e < 4; ++e) {
           const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
           const int i = e >> 1;
-          const float v = (key >= row_lo[mt][i] && key <= row_hi[mt][i]) ? s[mt][j][e] * scale_log2 : -INFINITY;
+          const float v = (key >= row_lo[mt][i] && key <= row_hi[mt][i])
+                              ? fmaf(-row_slope[mt][i], (float)(row_hi[mt][i] - key), s[mt][j][e] * scale_log2) : -INFINITY;
           s[mt][j][e] = v;
           mx[i] = fmaxf(mx[i], v);
         }
@@ -330,7 +333,8 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
     const bf16* __restrict__ kv_pages, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int nq, int nkv, int page_size,
-    int n_pages, int window, int chunk, float scale_log2, int tokens_per_block, const float* __restrict__ sinks) {
+    int n_pages, int window, int chunk, float scale_log2, int tokens_per_block, const float* __restrict__ sinks,
+    const float* __restrict__ slopes) {
   constexpr int PF_ROWS = 64 * MTW;                          // rows (token x head of the group) per block
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qbuf = reinterpret_cast<bf16*>(smem_raw);            // [PF_ROWS rows]
@@ -369,12 +373,14 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
   }
 
   int row_lo[MTW][2], row_hi[MTW][2];
+  float row_slope[MTW][2];                                   // per position of distance, in the units of the scores (log2)
 #pragma unroll
   for (int mt = 0; mt < MTW; ++mt)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int R = warp * WROWS + mt * 16 + (lane >> 2) + 8 * i;
       const int tq = R / G;
+      row_slope[mt][i] = slopes ? slopes[kvh * G + (R - tq * G)] * LOG2E : 0.f;
       if (tq < tq_n) {
         row_hi[mt][i] = pos0 + tq;
         row_lo[mt][i] = nhv_first_key(row_hi[mt][i], window, chunk);
@@ -420,7 +426,7 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
     const int key_base = key_begin + it * BN;
     if (key_base <= w_hi && key_base + BN > w_lo)
       warp_tile_prefill<MTW>(st, qbuf, warp * WROWS, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, key_base, row_lo,
-                        row_hi, w_lo, w_hi, scale_log2);
+                        row_hi, w_lo, w_hi, scale_log2, row_slope);
     __syncthreads();
   }
 #pragma unroll
@@ -520,7 +526,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int n_seqs, int nq, int nkv,
     int page_size, int n_pages, int window, int chunk, float scale_log2, int max_pieces, const FusedQK fq,
-    const float* __restrict__ sinks) {
+    const float* __restrict__ sinks, const float* __restrict__ slopes) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
   bf16* vbuf = kbuf + DSTAGES * TILE_ELEMS;
@@ -667,10 +673,13 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     uint32_t qf[KS][4];
     load_q_frags(qf, qbuf, 0);
     int row_lo[2], row_hi[2];
+    float row_slope[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
+      const int R = (lane >> 2) + 8 * i;
       row_lo[i] = lo;
-      row_hi[i] = (lane >> 2) + 8 * i < gn ? total - 1 : -1;
+      row_hi[i] = R < gn ? total - 1 : -1;
+      row_slope[i] = slopes && R < gn ? slopes[kvh * G + g0 + R] * LOG2E : 0.f;
     }
     RowState st;
     init_state(st);
@@ -698,7 +707,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
         __syncthreads();
       }
       if (key_base + warp * 16 < total && key_base + warp * 16 + 16 > lo)
-        warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2);
+        warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2, row_slope);
       __syncthreads();
     }
     cp_async_wait<0>();
@@ -841,7 +850,7 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
                             int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                             int nkv, int page_size, int n_pages, int window, int chunk, float scale, float* scratch_o,
                             float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                            const FusedQK& fq, const float* sinks, cudaStream_t stream) {
+                            const FusedQK& fq, const float* sinks, const float* slopes, cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
   ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0 &&
@@ -881,12 +890,12 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
       if (wide)
         nhv_launch(attn_prefill_kernel<2>, grid, THREADS, prefill_smem_bytes<2>(), stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-            n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks);
+            n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks, slopes);
     }
     if (!wide)
       nhv_launch(attn_prefill_kernel<1>, grid, THREADS, prefill_smem_bytes<1>(), stream,
           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-          n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks);
+          n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks, slopes);
   }
   if (n_decode_seqs > 0) {
     ATT_REQUIRE(scratch_o && scratch_ml && counters && max_pieces > 0 && decode_blocks > 0,
@@ -903,7 +912,7 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
     decode_blocks = resident;
     nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, max_pieces, fq, sinks);
+        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, max_pieces, fq, sinks, slopes);
   }
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
@@ -918,11 +927,11 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
                                    int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                                    int nkv, int page_size, int n_pages, int window, int chunk, float scale, float* scratch_o,
                                    float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                                   const float* sinks, cudaStream_t stream) {
+                                   const float* sinks, const float* slopes, cudaStream_t stream) {
   FusedQK none = {};
   return attention_launch(q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs,
                           n_prefill_tokens, n_prefill_seqs, n_decode_seqs, nq, nkv, page_size, n_pages, window, chunk, scale,
-                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, sinks, stream);
+                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, sinks, slopes, stream);
 }
 
 // 1 if this head size has the form of the decode kernel that works from the projection's output.
@@ -959,5 +968,5 @@ NHV_API int NHV_FN(nhv_attn_mma_decode_fused_d)(const void* qkv, int qkv_stride,
   fq.weight_offset = weight_offset;
   return attention_launch(qkv, qkv_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs, 0, 0,
                           n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale, scratch_o, scratch_ml, counters, max_pieces,
-                          1, fq, nullptr, stream);
+                          1, fq, nullptr, nullptr, stream);
 }

@@ -268,7 +268,8 @@ def planted_qk(g, L, nq, nkv, dk, window, dtype):
     (4, 2, 16, 24, 8, 12, 2, False, True), (6, 6, 8, 8, 5, 33, 2, False, True), (3, 1, 32, 16, 16, 7, 2, False, True),
     (4, 4, 64, 64, 64, 40, 2, False, True), (8, 2, 128, 128, 64, 100, 2, True, True), (2, 2, 64, 64, 16, 1, 2, False, True),
     (3, 1, 48, 40, 8, 0, 1, True, False), (5, 1, 16, 12, 3, 0, 1, True, False), (2, 1, 80, 64, 64, 0, 1, True, False),
-    (4, 1, 24, 24, 16, 9, 1, False, True)])
+    (4, 1, 24, 24, 16, 9, 1, False, True), (2, 1, 320, 288, 16, 0, 1, True, False), (4, 1, 576, 512, 64, 0, 1, True, False),
+    (2, 1, 1040, 1030, 8, 0, 1, False, False)])
 def test_attention_kernels_in_portions_against_plain(ops, dtype, simt, nq, nkv, dk, dv, page, window, planes, sink, slope):
     """Portions that start and end inside windows and pages, single tokens (a decoded token whose window's edge lies
     on a page border among them), a request of two tokens and one of several hundred; pages in shuffled places of a
@@ -338,7 +339,7 @@ def latent_spec(H, dn, dr, dv, q_rank, rank, base, scale, eps, sink=True):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,dn,dr,dv,q_rank,rank,width,page", [
     (3, 24, 8, 20, 48, 40, 96, 8), (5, 8, 4, 8, 16, 12, 64, 5), (2, 16, 16, 32, 24, 64, 80, 16), (3, 10, 6, 14, 18, 22, 100, 3),
-    (1, 64, 32, 64, 96, 128, 128, 64)])
+    (1, 64, 32, 64, 96, 128, 128, 64), (2, 32, 32, 48, 64, 272, 128, 16)])
 def test_latent_attention_part(dtype, H, dn, dr, dv, q_rank, rank, width, page):
     """Whole against portions in unequal batches, in a pool that only holds what is live.  The sinks are large, so a
     sink that is left out, counted per key or scaled moves every output; the rotated key part is made loud, so a
