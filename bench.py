@@ -842,7 +842,7 @@ def bench_designs(args) -> dict:
             for _ in range(max(args.warmup, 3)):
                 decode()
             torch.cuda.synchronize()
-            steps = min(args.steps, page - 8)
+            steps = min(args.steps, page - 24)
             e0.record()
             for _ in range(steps):
                 decode()
@@ -856,6 +856,26 @@ def bench_designs(args) -> dict:
                 + runner.layout.state_bytes_per_slot(torch.bfloat16) * batch * 2
             out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 3), "tok_s": round(batch / ms * 1e3),
                                        "hbm_frac_of_measured": round(read / (ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)}
+            # the same step without its graph, events around every launch (the gaps of an eager run count too)
+            del events[:]
+            for name, fn in stock.items():
+                setattr(ops, name, timed(name, fn))
+            try:
+                for _ in range(reps):
+                    items = []
+                    for i in ids:
+                        runner.cache.allocate(i, lens[i] + 1)
+                        items.append(StepItem(i, [1], lens[i], [0]))
+                        lens[i] += 1
+                    runner.step(items)
+                torch.cuda.synchronize()
+            finally:
+                for name, fn in stock.items():
+                    setattr(ops, name, fn)
+            kinds_us = {}
+            for kind, a, b in events:
+                kinds_us[kind] = kinds_us.get(kind, 0.0) + a.elapsed_time(b) * 1e3 / reps
+            out[f"decode_b{batch}"]["eager_us_by_kind"] = {k: round(v, 1) for k, v in sorted(kinds_us.items(), key=lambda kv: -kv[1])}
             for i in ids:
                 runner.cache.free(i)
         del llm, runner

@@ -135,28 +135,33 @@ NHV_API int nhv_clamped_glu(int dtype, void* out, const void* gate_up, int n_row
 }
 
 // out[t, c] = x[t, c] * sigmoid(g[t, c / group]): one gate per head of `group` columns.  out may be x itself.
+// x_head: the distance between two heads in a row of x (group where the heads are packed; more where each head is
+// padded, as the output of attention over padded heads is).
 template <typename T>
 __global__ void sigmoid_mul_heads_kernel(T* out, int out_stride, const T* x, int x_stride, const T* __restrict__ g,
-                                         int g_stride, int width, int group, size_t total) {
+                                         int g_stride, int width, int group, int x_head, size_t total) {
   pdl_prologue();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / width;
     const int c = (int)(i - t * width);
-    out[t * out_stride + c] = from_f32<T>(to_f32<T>(x[t * x_stride + c]) * sigmoid_f(to_f32<T>(g[t * g_stride + c / group])));
+    const int h = c / group;
+    out[t * out_stride + c] = from_f32<T>(to_f32<T>(x[t * x_stride + (size_t)h * x_head + (c - h * group)]) *
+                                          sigmoid_f(to_f32<T>(g[t * g_stride + h])));
   }
 }
 
 NHV_API int nhv_sigmoid_mul_heads(int dtype, void* out, int out_stride, const void* x, int x_stride, const void* g,
-                                  int g_stride, int n_rows, int width, int group, cudaStream_t stream) {
+                                  int g_stride, int n_rows, int width, int group, int x_head, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  NHV_REQUIRE(n_rows > 0 && width > 0 && group > 0 && width % group == 0, "sigmoid_mul_heads: %d columns do not divide into heads of %d", width, group);
+  NHV_REQUIRE(n_rows > 0 && width > 0 && group > 0 && width % group == 0 && x_head >= group,
+              "sigmoid_mul_heads: %d columns do not divide into heads of %d", width, group);
   const size_t total = (size_t)n_rows * width;
   if (dtype == NHV_F32)
     nhv_launch(sigmoid_mul_heads_kernel<float>, gating_blocks(total), 256, 0, stream, (float*)out, out_stride, (const float*)x,
-               x_stride, (const float*)g, g_stride, width, group, total);
+               x_stride, (const float*)g, g_stride, width, group, x_head, total);
   else if (dtype == NHV_BF16)
     nhv_launch(sigmoid_mul_heads_kernel<__nv_bfloat16>, gating_blocks(total), 256, 0, stream, (__nv_bfloat16*)out, out_stride,
-               (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)g, g_stride, width, group, total);
+               (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)g, g_stride, width, group, x_head, total);
   else
     NHV_REQUIRE(false, "sigmoid_mul_heads: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("sigmoid_mul_heads");

@@ -92,8 +92,18 @@ __global__ void general_delta_prepare_kernel(float* __restrict__ vec, float* __r
   }
 }
 
-// R: rows of a column per lane (a multiple of 4, 8 R >= d).
-template <int R>
+__device__ __forceinline__ void gd_cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void gd_cp_async8(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void gd_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void gd_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// R: rows of a column per lane (a multiple of 4, 8 R >= d).  ASYNC (d a multiple of 4): the tokens reach shared memory
+// by cp.async, 16 at a time, the next 16 while these are worked on; otherwise by plain loads, one stage.
+template <int R, bool ASYNC>
 __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
     float* __restrict__ o_out, const float* __restrict__ vec, const float* __restrict__ sc, const float* __restrict__ v32,
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
@@ -101,6 +111,7 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
   extern __shared__ __align__(16) float smem[];
   pdl_prologue();
   constexpr int DP = R * GD_LANES;                    // a vector in shared memory: d floats, then zeros
+  constexpr int STAGE = 5 * GD_CHUNK * DP + GD_CHUNK * GD_COLS + GD_CHUNK * 2;
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GD_COLS;
   const int first = cu_q[s], n = cu_q[s + 1] - first;
   const int slot = slots[s];
@@ -111,9 +122,6 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
       o_out[((size_t)(first + i / ncol) * H + h) * d + col0 + i % ncol] = 0.f;
     return;
   }
-  float* vs_u = smem;                                 // [5][CHUNK][DP]: u, a*u, r*w, w, k
-  float* vs_v = smem + 5 * GD_CHUNK * DP;             // [CHUNK][COLS]
-  float* vs_s = vs_v + GD_CHUNK * GD_COLS;            // [CHUNK][2]
   const int cl = tid / GD_LANES, part = tid % GD_LANES;
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
@@ -128,21 +136,66 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
       S[4 * j + e] = (live && !fresh && i < d) ? st[i] : 0.f;
     }
   const size_t plane = (size_t)n_tokens * H * d;
-  for (int c0 = 0; c0 < n; c0 += GD_CHUNK) {
+  if constexpr (ASYNC) {                              // what no copy writes: the zeros behind a vector, the columns past d
+    for (int i = tid; i < 2 * STAGE; i += GD_THREADS) smem[i] = 0.f;
+    __syncthreads();
+  }
+  // tokens [c0, c0 + cn) of the request into a stage: [5][CHUNK][DP] u, a*u, r*w, w, k; [CHUNK][COLS] v; [CHUNK][2]
+  auto fetch = [&](int c0, int stage) {
+    float* base = smem + stage * STAGE;
     const int cn = min(GD_CHUNK, n - c0);
-    __syncthreads();
-    for (int i = tid; i < 5 * cn * DP; i += GD_THREADS) {
-      const int which = i / (cn * DP), rem = i - which * (cn * DP);
-      const int tt = rem / DP, c = rem - tt * DP;
-      vs_u[(which * GD_CHUNK + tt) * DP + c] =
-          c < d ? vec[which * plane + ((size_t)(first + c0 + tt) * H + h) * d + c] : 0.f;
+    if constexpr (ASYNC) {
+      const int quads = d >> 2, per = cn * quads;
+      for (int i = tid; i < 5 * per; i += GD_THREADS) {
+        const int which = i / per, rem = i - which * per;
+        const int tt = rem / quads, c = rem - tt * quads;
+        gd_cp_async16(base + (which * GD_CHUNK + tt) * DP + 4 * c,
+                      vec + which * plane + ((size_t)(first + c0 + tt) * H + h) * d + 4 * c);
+      }
+      const int vq = ncol >> 2;
+      for (int i = tid; i < cn * vq; i += GD_THREADS) {
+        const int tt = i / vq, c = i - tt * vq;
+        gd_cp_async16(base + 5 * GD_CHUNK * DP + tt * GD_COLS + 4 * c,
+                      v32 + ((size_t)(first + c0 + tt) * H + h) * d + col0 + 4 * c);
+      }
+      for (int tt = tid; tt < cn; tt += GD_THREADS)
+        gd_cp_async8(base + 5 * GD_CHUNK * DP + GD_CHUNK * GD_COLS + tt * 2, sc + ((size_t)(first + c0 + tt) * H + h) * 2);
+    } else {
+      for (int i = tid; i < 5 * cn * DP; i += GD_THREADS) {
+        const int which = i / (cn * DP), rem = i - which * (cn * DP);
+        const int tt = rem / DP, c = rem - tt * DP;
+        base[(which * GD_CHUNK + tt) * DP + c] =
+            c < d ? vec[which * plane + ((size_t)(first + c0 + tt) * H + h) * d + c] : 0.f;
+      }
+      for (int i = tid; i < cn * GD_COLS; i += GD_THREADS) {
+        const int tt = i / GD_COLS, c = i - tt * GD_COLS;
+        base[5 * GD_CHUNK * DP + i] = c < ncol ? v32[((size_t)(first + c0 + tt) * H + h) * d + col0 + c] : 0.f;
+      }
+      for (int i = tid; i < cn * 2; i += GD_THREADS)
+        base[5 * GD_CHUNK * DP + GD_CHUNK * GD_COLS + i] = sc[((size_t)(first + c0 + (i >> 1)) * H + h) * 2 + (i & 1)];
     }
-    for (int i = tid; i < cn * GD_COLS; i += GD_THREADS) {
-      const int tt = i / GD_COLS, c = i - tt * GD_COLS;
-      vs_v[i] = c < ncol ? v32[((size_t)(first + c0 + tt) * H + h) * d + col0 + c] : 0.f;
+  };
+  const int n_chunks = (n + GD_CHUNK - 1) / GD_CHUNK;
+  if constexpr (ASYNC) {
+    fetch(0, 0);
+    gd_cp_async_commit();
+  }
+  for (int ci = 0; ci < n_chunks; ++ci) {
+    const int c0 = ci * GD_CHUNK;
+    const int cn = min(GD_CHUNK, n - c0);
+    const int stage = ASYNC ? (ci & 1) : 0;
+    if constexpr (ASYNC) {
+      if (ci + 1 < n_chunks) fetch(c0 + GD_CHUNK, stage ^ 1);
+      gd_cp_async_commit();                           // one group per pass, empty or not
+      gd_cp_async_wait<1>();
+    } else {
+      __syncthreads();
+      fetch(c0, 0);
     }
-    for (int i = tid; i < cn * 2; i += GD_THREADS) vs_s[i] = sc[((size_t)(first + c0) * H) * 2 + (size_t)(i >> 1) * H * 2 + h * 2 + (i & 1)];
     __syncthreads();
+    const float* vs_u = smem + stage * STAGE;
+    const float* vs_v = vs_u + 5 * GD_CHUNK * DP;
+    const float* vs_s = vs_v + GD_CHUNK * GD_COLS;
     for (int tt = 0; tt < cn; ++tt) {
       const float* base = vs_u + tt * DP + 4 * part;
       float A = 0.f, B = 0.f;
@@ -175,7 +228,9 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
       if (live && part == 0)
         o_out[((size_t)(first + c0 + tt) * H + h) * d + col] = fmaf(vt, vs_s[tt * 2 + 1], fmaf(-A, vs_s[tt * 2], B));
     }
+    if constexpr (ASYNC) __syncthreads();             // the stage is free for the fetch after next
   }
+  if constexpr (ASYNC) gd_cp_async_wait<0>();
   if (live) {
 #pragma unroll
     for (int j = 0; j < R / 4; ++j)
@@ -214,20 +269,29 @@ NHV_API int nhv_general_delta(int dtype, float* o_out, const void* proj, int pro
     NHV_REQUIRE(false, "general_delta: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("general_delta_prepare");
   dim3 grid(n_seqs, H, (d + GD_COLS - 1) / GD_COLS);
-#define SCAN(R)                                                                                                     \
+  // cp.async wants 16-byte aligned sources: d a multiple of 4 and scratch that starts on such a boundary
+  const bool async = d % 4 == 0 && (((uintptr_t)vec | (uintptr_t)sc | (uintptr_t)v32) & 15) == 0;
+#define SCAN_AS(R, A)                                                                                               \
   do {                                                                                                              \
-    const size_t smem = (size_t)(5 * GD_CHUNK * R * GD_LANES + GD_CHUNK * GD_COLS + GD_CHUNK * 2) * sizeof(float);  \
+    const size_t smem = (size_t)(A ? 2 : 1) * (5 * GD_CHUNK * R * GD_LANES + GD_CHUNK * GD_COLS + GD_CHUNK * 2) *   \
+                        sizeof(float);                                                                              \
     if (smem > 48 * 1024)                                                                                           \
-      NHV_CUDA(cudaFuncSetAttribute(general_delta_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+      NHV_CUDA(cudaFuncSetAttribute(general_delta_scan_kernel<R, A>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                     (int)smem), "general_delta");                                                   \
-    nhv_launch(general_delta_scan_kernel<R>, grid, GD_THREADS, smem, stream, o_out, (const float*)vec,              \
+    nhv_launch(general_delta_scan_kernel<R, A>, grid, GD_THREADS, smem, stream, o_out, (const float*)vec,           \
                (const float*)sc, (const float*)v32, state, state_stride, cu_q, q_start, slots, n_tokens, H, d);     \
+  } while (0)
+#define SCAN(R)              \
+  do {                       \
+    if (async) SCAN_AS(R, true); \
+    else SCAN_AS(R, false);  \
   } while (0)
   if (d <= 32) SCAN(4);
   else if (d <= 64) SCAN(8);
   else if (d <= 128) SCAN(16);
   else SCAN(32);
 #undef SCAN
+#undef SCAN_AS
   NHV_CHECK_LAUNCH("general_delta_scan");
   return 0;
 }

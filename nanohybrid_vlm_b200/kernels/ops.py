@@ -345,13 +345,52 @@ def general_delta(o, proj, aw, a_bias, w2, w0, state, batch, H: int, d: int, dec
          float(decay_floor), stream_ptr())
 
 
-def sigmoid_mul_heads(out, x, gate, group: int) -> None:
-    """out[t, c] = x[t, c] * sigmoid(gate[t, c // group]): one gate per head of ``group`` columns, in 32-bit."""
+def sigmoid_mul_heads(out, x, gate, group: int, x_head: int | None = None) -> None:
+    """out[t, c] = x[t, c] * sigmoid(gate[t, c // group]): one gate per head of ``group`` columns, in 32-bit.
+    ``x_head``: the distance between two heads in a row of x, where x holds padded heads (x [T, heads * x_head])."""
     _need_cuda(out, x, gate)
-    assert out.shape == x.shape and out.dim() == 2 and out.dtype == x.dtype == gate.dtype and x.shape[1] % group == 0
-    assert gate.shape == (x.shape[0], x.shape[1] // group) and out.stride(1) == x.stride(1) == gate.stride(1) == 1
+    heads = out.shape[1] // group
+    assert out.dim() == 2 and out.dtype == x.dtype == gate.dtype and out.shape[1] % group == 0
+    assert x.shape == ((out.shape[0], heads * x_head) if x_head else out.shape)
+    assert gate.shape == (out.shape[0], heads) and out.stride(1) == x.stride(1) == gate.stride(1) == 1
     call("nhv_sigmoid_mul_heads", dtype_code(out), out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), gate.data_ptr(),
-         gate.stride(0), x.shape[0], x.shape[1], int(group), stream_ptr())
+         gate.stride(0), out.shape[0], out.shape[1], int(group), int(x_head or group), stream_ptr())
+
+
+LATENT_TILE = 64        # rows of a temporary page of expanded keys and values
+
+
+def latent_expand(pages, tables, batch, q, q_lat, ukv, H: int, dn: int, dr: int, dv: int, rank: int, D: int):
+    """Attention over one latent per token, prepared for the tensor-core kernels: the latents of the step's requests
+    (all their tokens in the cache) are expanded by ``ukv`` [H dn + H dv, rank] into a key [dn | rotated part dr | 0]
+    and a value [dv | 0] per head, padded to D elements, in temporary pages of 64 tokens; the queries likewise.
+    Returns (queries [T, H D], temporary pages [n, 2, H, 64, D], their block tables [requests, pages])."""
+    _need_cuda(pages, q, q_lat, ukv)
+    T, row = q.shape[0], pages.shape[-1]
+    plan = getattr(batch, "_latent_rows", None)
+    if plan is None or plan[3] != batch.host_kv_len:        # every such layer of the step uses the same rows
+        counts = [-(-n // LATENT_TILE) for n in batch.host_kv_len]
+        first, width = [0], max(counts)
+        for c in counts:
+            first.append(first[-1] + c)
+        table = [[first[s] + i if i < counts[s] else -1 for i in range(width)] for s in range(len(counts))]
+        plan = (torch.tensor([f * LATENT_TILE for f in first[:-1]], dtype=torch.int32).to(q.device, non_blocking=True),
+                torch.tensor(table, dtype=torch.int32).to(q.device, non_blocking=True), first[-1], list(batch.host_kv_len))
+        batch._latent_rows = plan
+    row0, tmp_table, n_tmp = plan[:3]
+    rows = n_tmp * LATENT_TILE
+    lat = torch.empty(rows, rank, dtype=q.dtype, device=q.device)
+    kr = torch.empty(rows, max(dr, 1), dtype=q.dtype, device=q.device)
+    call("nhv_latent_gather", dtype_code(q), lat.data_ptr(), kr.data_ptr(), pages.data_ptr(), tables.block_tables.data_ptr(),
+         tables.block_tables.stride(0), batch.kv_len.data_ptr(), row0.data_ptr(), batch.n_seqs, batch.max_kv_len, rank, dr,
+         row, pages.shape[3], pages.shape[0], stream_ptr())
+    kv = torch.empty(rows, ukv.shape[0], dtype=q.dtype, device=q.device)
+    linear(kv, lat, ukv)
+    tmp = torch.empty(n_tmp, 2, H, LATENT_TILE, D, dtype=q.dtype, device=q.device)
+    qp = torch.empty(T, H * D, dtype=q.dtype, device=q.device)
+    call("nhv_latent_assemble", dtype_code(q), tmp.data_ptr(), qp.data_ptr(), kv.data_ptr(), kr.data_ptr(), q.data_ptr(),
+         q.stride(0), q_lat.data_ptr(), q_lat.stride(0), rows, T, H, dn, dr, dv, rank, D, stream_ptr())
+    return qp, tmp, tmp_table
 
 
 def relu_squared(x) -> None:

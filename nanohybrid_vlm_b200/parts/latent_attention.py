@@ -16,10 +16,18 @@ kernel reads a row as key and its first kv_rank elements as value, and its outpu
 Tensors: ``dq`` [q_rank, width], ``dq.norm`` [q_rank], ``uq`` [H (dn + dr), q_rank], ``dkvg`` [kv_rank + dr (+ H), width]
 packed from the checkpoint's ``dkv`` and ``g``, ``dkv.norm`` [kv_rank], ``uk`` [H dn, kv_rank], ``uv`` [H dv, kv_rank],
 ``sink`` [H] (float32), ``o`` [width, H dv].  Norms, rotation, scores and softmax are computed in 32-bit.
+
+Two forms of one step.  Single tokens (and float32) attend over the latents as above.  A bfloat16 step with prompt
+portions expands the latents of its requests into keys [uk_h c | k_r] and values uv_h c per head, padded to a common
+head size D, in temporary pages, and runs the tensor-core attention kernels over those: a query then costs
+dn + dr + dv operations per key and head instead of 2 kv_rank + dr, and the expansion is one product over the
+requests' tokens.  The two forms differ by rounding only (which of the factors is rounded to bfloat16 on the way).
 """
 from __future__ import annotations
 
-from ..kernels import ops
+import torch
+
+from ..kernels import attention_mma, ops
 from .base import MIXERS, Mixer, PagedKVNeed
 from .spec import ParamDecl, Source
 
@@ -63,6 +71,11 @@ class LatentAttention(Mixer):
         # uk per head with the latent along the rows, so that uk_h^T q_h is a product of the usual form
         self.uk_t = self.w_uk.view(self.H, self.dn, self.rank).transpose(1, 2).contiguous() if self.dn else None
         self.uv_heads = self.w_uv.view(self.H, self.dv, self.rank)
+        # the expanded form: both expansions as one matrix, heads padded to a size the tensor-core kernels take
+        self.D = -(-max(self.dn + self.dr, self.dv) // 16) * 16
+        self.ukv = None
+        if self.w_uk.dtype == torch.bfloat16 and self.w_uk.is_cuda and attention_mma.supports(self.D, self.H, self.H):
+            self.ukv = torch.cat([self.w_uk, self.w_uv]).contiguous()
 
     def cache_need(self):
         return PagedKVNeed(1, self.row, v_head_dim=self.rank, planes=1)
@@ -86,6 +99,10 @@ class LatentAttention(Mixer):
         ops.latent_rope_store(kvg[:, :self.row], q, q_lat, cache.pages if cache.writes else None,
                               cache.tables.slot_mapping, batch.positions, table, rotary_dim, H, self.dn, self.dr,
                               self.rank, self.eps, self.w_dkv_norm)
+        gate = kvg[:, self.row:] if self.gate else None
+        if (self.ukv is not None and EXPAND_PROMPT_PORTIONS and batch.n_prefill_tokens > 0
+                and attention_mma.supports(self.D, H, H, batch.n_seqs)):
+            return self._expanded(q, q_lat, gate, batch, cache)
         if self.dn:
             ops.linear_heads(q_lat.view(T, H, self.row)[:, :, :self.rank], q.view(T, H, self.dn + self.dr)[:, :, :self.dn],
                              self.uk_t)
@@ -98,10 +115,32 @@ class LatentAttention(Mixer):
         o = self.new(T, H * self.dv)
         ops.linear_heads(o.view(T, H, self.dv), o_lat.view(T, H, self.rank), self.uv_heads)
         if self.gate:
-            ops.sigmoid_mul_heads(o, o, kvg[:, self.row:], self.dv)
+            ops.sigmoid_mul_heads(o, o, gate, self.dv)
         y = self.new(T, self.env.hidden_size)
         ops.linear(y, o, self.w_o)
         return y
+
+    def _expanded(self, q, q_lat, gate, batch, cache):
+        """The step's attention over keys and values expanded per head (bfloat16 steps that bring prompt portions;
+        their single tokens ride along)."""
+        T, H, D = q.shape[0], self.H, self.D
+        qp, pages, tables = ops.latent_expand(cache.pages, cache.tables, batch, q, q_lat, self.ukv, H, self.dn, self.dr,
+                                              self.dv, self.rank, D)
+        padded = self.new(T, H * D)
+        ops.attention_tensor_core(padded, qp, pages, tables, batch.cu_q, batch.kv_len, batch.n_seqs,
+                                  batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len, H, H,
+                                  D, self.scale, 0, self.w_sink if self.has_sink else None)
+        o = self.new(T, H * self.dv)
+        if self.gate:
+            ops.sigmoid_mul_heads(o, padded, gate, self.dv, x_head=D)
+        else:
+            o.view(T, H, self.dv).copy_(padded.view(T, H, D)[:, :, :self.dv])
+        y = self.new(T, self.env.hidden_size)
+        ops.linear(y, o, self.w_o)
+        return y
+
+
+EXPAND_PROMPT_PORTIONS = True       # tests switch it off to compare the two forms
 
 
 MIXERS.register("latent_attention", LatentAttention)

@@ -340,11 +340,15 @@ def latent_spec(H, dn, dr, dv, q_rank, rank, base, scale, eps, sink=True):
 @pytest.mark.parametrize("H,dn,dr,dv,q_rank,rank,width,page", [
     (3, 24, 8, 20, 48, 40, 96, 8), (5, 8, 4, 8, 16, 12, 64, 5), (2, 16, 16, 32, 24, 64, 80, 16), (3, 10, 6, 14, 18, 22, 100, 3),
     (1, 64, 32, 64, 96, 128, 128, 64), (2, 32, 32, 48, 64, 272, 128, 16)])
-def test_latent_attention_part(dtype, H, dn, dr, dv, q_rank, rank, width, page):
+@pytest.mark.parametrize("expand", [True, False], ids=["expanded_prompts", "latents_only"])
+def test_latent_attention_part(dtype, expand, H, dn, dr, dv, q_rank, rank, width, page, monkeypatch):
     """Whole against portions in unequal batches, in a pool that only holds what is live.  The sinks are large, so a
-    sink that is left out, counted per key or scaled moves every output; the rotated key part is made loud, so a
-    wrong angle, pairing or position shows."""
+    sink that is left out, counted per key or scaled moves every output.  In bfloat16 a step with prompt portions
+    expands the latents into keys and values per head for the tensor-core kernels (single tokens of the same step
+    ride along), a step of single tokens attends over the latents; both forms are run for every step shape."""
     from nanohybrid_vlm_b200.parts import MIXERS
+    from nanohybrid_vlm_b200.parts import latent_attention as la
+    monkeypatch.setattr(la, "EXPAND_PROMPT_PORTIONS", expand)
     eps, base, scale = 1e-5, 5000.0, 0.2
     mixer, w = make_part(MIXERS, latent_spec(H, dn, dr, dv, q_rank, rank, base, scale, eps), width, dtype, seed=H * 7 + dn,
                          scale={"sink": 2.0})
