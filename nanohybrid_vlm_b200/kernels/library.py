@@ -65,6 +65,8 @@ _SIGNATURES = {
     "nhv_sigmoid_mul_heads": [I, P, I, P, I, P, I, I, I, I, I, P],
     "nhv_latent_gather": [I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
     "nhv_latent_assemble": [I, P, P, P, P, P, I, P, I, ctypes.c_long, I, I, I, I, I, I, I, P],
+    "nhv_latent_decode_supports": [I, I, I],
+    "nhv_latent_decode": [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, P, I, P, P, P],
     "nhv_relu_squared": [I, P, c_size_t, P],
     "nhv_scale_softcap": [P, F, F, c_size_t, P],
 }

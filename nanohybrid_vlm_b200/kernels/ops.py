@@ -393,6 +393,34 @@ def latent_expand(pages, tables, batch, q, q_lat, ukv, H: int, dn: int, dr: int,
     return qp, tmp, tmp_table
 
 
+LATENTS_ON_TENSOR_CORES = True      # tests switch it off to compare with the CUDA-core kernel at the same shapes
+
+
+def latent_attention(out, q_lat, pages, tables, batch, H: int, rank: int, row: int, scale: float, sinks=None) -> None:
+    """Attention of the step's tokens over one latent per token: pages with one plane whose rows [row] are the key of
+    every head and whose leading ``rank`` elements are the value of every head; q_lat [T, H row] -> out [T, H rank].
+    ``sinks`` [H] float32: exp(sink) joins each head's softmax denominator once.  bfloat16 with rows and latents in
+    steps of 8 runs on the tensor cores, a token's keys shared between blocks and merged (scratch: one partial result
+    per token, head and piece); float32 and other sizes run the CUDA-core kernel."""
+    _need_cuda(out, q_lat, pages, sinks)
+    T = q_lat.shape[0]
+    if not (LATENTS_ON_TENSOR_CORES and q_lat.dtype == torch.bfloat16 and pages.shape[1] == 1 and pages.shape[2] == 1
+            and pages.shape[-1] == row and library.load_library().nhv_latent_decode_supports(H, rank, row)):
+        attention_sink_simt(out, q_lat, pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
+                            H, 1, row, rank, scale, sinks)
+        return
+    _contig("kv_pages", pages)
+    assert q_lat.shape == (T, H * row) and out.shape == (T, H * rank) and out.dtype == pages.dtype == torch.bfloat16
+    assert q_lat.stride(1) == 1 and out.stride(1) == 1 and sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == H)
+    tiles = -(-batch.max_kv_len // 64)
+    pieces = max(1, min(tiles, 64, -(-2 * 148 // (T * -(-H // 16)))))
+    part = torch.empty(T * H * pieces * (rank + 2), dtype=torch.float32, device=out.device)
+    call("nhv_latent_decode", out.data_ptr(), out.stride(0), q_lat.data_ptr(), q_lat.stride(0), pages.data_ptr(),
+         tables.block_tables.data_ptr(), tables.block_tables.stride(0), batch.cu_q.data_ptr(), batch.kv_len.data_ptr(),
+         batch.n_seqs, T, H, rank, row, pages.shape[3], pages.shape[0], float(scale), _ptr(sinks), pieces,
+         part.data_ptr(), part.data_ptr() + 4 * T * H * pieces * rank, stream_ptr())
+
+
 def relu_squared(x) -> None:
     """x = max(x, 0) ** 2 in place."""
     _need_cuda(x)

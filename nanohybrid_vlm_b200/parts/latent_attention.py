@@ -109,9 +109,8 @@ class LatentAttention(Mixer):
         else:
             q_lat.view(T, H, self.row)[:, :, :self.rank].zero_()
         o_lat = self.new(T, H * self.rank)
-        ops.attention_sink_simt(o_lat, q_lat, cache.pages, cache.tables.block_tables, batch.cu_q, batch.kv_len,
-                                batch.n_seqs, batch.n_tokens, H, 1, self.row, self.rank, self.scale,
-                                self.w_sink if self.has_sink else None)
+        ops.latent_attention(o_lat, q_lat, cache.pages, cache.tables, batch, H, self.rank, self.row, self.scale,
+                             self.w_sink if self.has_sink else None)
         o = self.new(T, H * self.dv)
         ops.linear_heads(o.view(T, H, self.dv), o_lat.view(T, H, self.rank), self.uv_heads)
         if self.gate:

@@ -269,7 +269,7 @@ def planted_qk(g, L, nq, nkv, dk, window, dtype):
     (4, 4, 64, 64, 64, 40, 2, False, True), (8, 2, 128, 128, 64, 100, 2, True, True), (2, 2, 64, 64, 16, 1, 2, False, True),
     (3, 1, 48, 40, 8, 0, 1, True, False), (5, 1, 16, 12, 3, 0, 1, True, False), (2, 1, 80, 64, 64, 0, 1, True, False),
     (4, 1, 24, 24, 16, 9, 1, False, True), (2, 1, 320, 288, 16, 0, 1, True, False), (4, 1, 576, 512, 64, 0, 1, True, False),
-    (2, 1, 1040, 1030, 8, 0, 1, False, False)])
+    (2, 1, 1040, 1030, 8, 0, 1, False, False), (20, 1, 72, 56, 16, 0, 1, True, False), (16, 1, 32, 32, 4, 0, 1, False, False)])
 def test_attention_kernels_in_portions_against_plain(ops, dtype, simt, nq, nkv, dk, dv, page, window, planes, sink, slope):
     """Portions that start and end inside windows and pages, single tokens (a decoded token whose window's edge lies
     on a page border among them), a request of two tokens and one of several hundred; pages in shuffled places of a
@@ -315,6 +315,9 @@ def test_attention_kernels_in_portions_against_plain(ops, dtype, simt, nq, nkv, 
             ops.attention_sink_simt(out, dev(q), pages, dev(bt), b.cu_q, b.kv_len, len(who), q.shape[0], nq, nkv, dk, dv,
                                     scale, None if sinks is None else dev(sinks), window, 0,
                                     None if slopes is None else dev(slopes))
+        elif planes == 1 and not window and slopes is None:     # latents: the tensor-core kernel where the sizes allow it
+            ops.latent_attention(out, dev(q), pages, SimpleNamespace(block_tables=dev(bt)), b, nq, dv, dk, scale,
+                                 None if sinks is None else dev(sinks))
         else:       # the dispatcher: the tensor-core kernels where the shape allows them
             ops.attention_sink(out, dev(q), pages, SimpleNamespace(block_tables=dev(bt)), b, nq, nkv, dk, dv, scale,
                                None if sinks is None else dev(sinks), window, 0, None if slopes is None else dev(slopes))
@@ -339,16 +342,18 @@ def latent_spec(H, dn, dr, dv, q_rank, rank, base, scale, eps, sink=True):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,dn,dr,dv,q_rank,rank,width,page", [
     (3, 24, 8, 20, 48, 40, 96, 8), (5, 8, 4, 8, 16, 12, 64, 5), (2, 16, 16, 32, 24, 64, 80, 16), (3, 10, 6, 14, 18, 22, 100, 3),
-    (1, 64, 32, 64, 96, 128, 128, 64), (2, 32, 32, 48, 64, 272, 128, 16)])
-@pytest.mark.parametrize("expand", [True, False], ids=["expanded_prompts", "latents_only"])
-def test_latent_attention_part(dtype, expand, H, dn, dr, dv, q_rank, rank, width, page, monkeypatch):
+    (1, 64, 32, 64, 96, 128, 128, 64), (2, 32, 32, 48, 64, 272, 128, 16), (20, 16, 8, 16, 32, 48, 64, 16)])
+@pytest.mark.parametrize("form", ["expanded_prompts", "latents_tensor_cores", "latents_cuda_cores"])
+def test_latent_attention_part(ops, dtype, form, H, dn, dr, dv, q_rank, rank, width, page, monkeypatch):
     """Whole against portions in unequal batches, in a pool that only holds what is live.  The sinks are large, so a
     sink that is left out, counted per key or scaled moves every output.  In bfloat16 a step with prompt portions
     expands the latents into keys and values per head for the tensor-core kernels (single tokens of the same step
-    ride along), a step of single tokens attends over the latents; both forms are run for every step shape."""
+    ride along), a step of single tokens attends over the latents, on the tensor cores (a token's keys cut into
+    pieces that are merged) or the CUDA cores; every form is run for every step shape."""
     from nanohybrid_vlm_b200.parts import MIXERS
     from nanohybrid_vlm_b200.parts import latent_attention as la
-    monkeypatch.setattr(la, "EXPAND_PROMPT_PORTIONS", expand)
+    monkeypatch.setattr(la, "EXPAND_PROMPT_PORTIONS", form == "expanded_prompts")
+    monkeypatch.setattr(ops, "LATENTS_ON_TENSOR_CORES", form != "latents_cuda_cores")
     eps, base, scale = 1e-5, 5000.0, 0.2
     mixer, w = make_part(MIXERS, latent_spec(H, dn, dr, dv, q_rank, rank, base, scale, eps), width, dtype, seed=H * 7 + dn,
                          scale={"sink": 2.0})
