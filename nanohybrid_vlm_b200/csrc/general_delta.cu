@@ -3,9 +3,9 @@
 // Per head, with the state S [d, d] (fp32, carried per request; rows: key channels, columns: value channels):
 //   S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,     o_t = S_t^T r_t
 // where u_t = k_t / sqrt(sum k_t^2 + 1e-6) is the unit key, w_t a decay per key channel and a_t a removal rate per key
-// channel:  w_t = exp(-decay_floor * sigmoid(W2 tanh(z_t) + w0)),  a_t = sigmoid(y_t + b), with z_t [rank] and y_t [H d]
-// two small projections of the token that the caller gives in fp32.  Decay and removal both read the state of the
-// token before.
+// channel:  w_t = exp(-decay_floor * sigmoid(e_t + w0)),  a_t = sigmoid(y_t + b), with e_t = W2 tanh(z_t) and y_t [H d]
+// projections of the token that the caller gives in fp32 (z_t [rank] a small projection; general_delta_tanh makes
+// tanh(z_t) in the storage type for the product with W2).  Decay and removal both read the state of the token before.
 //
 // general_delta_prepare: one warp per (token, head): u, a * u, r * w, w, k widened to fp32, the two scalars
 //                r . (a * u) and r . k, and v in fp32.
@@ -26,21 +26,30 @@
 
 constexpr int GD_WARPS = 4;
 constexpr int GD_MAX_D = 256;
-constexpr int GD_MAX_RANK = 1024;
 constexpr int GD_CHUNK = 16;
 constexpr int GD_LANES = 8;
 constexpr int GD_THREADS = 128;
 constexpr int GD_COLS = GD_THREADS / GD_LANES;
 
-// proj [T, 4 n] rows of proj_stride: r, k, v (then the gate, not read here); aw [T, n + rank] fp32: y then z.
+// out[t, j] = tanh(in[t, j]) in the storage type, in [T, cols] fp32 with rows in_stride apart.
+template <typename T>
+__global__ void general_delta_tanh_kernel(T* __restrict__ out, const float* __restrict__ in, int in_stride, int cols,
+                                          size_t total) {
+  pdl_prologue();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / cols;
+    out[i] = from_f32<T>(tanhf(in[t * in_stride + (i - t * cols)]));
+  }
+}
+
+// proj [T, 4 n] rows of proj_stride: r, k, v (then the gate, not read here); aw [T, >= n] fp32: y; dec [T, n] fp32: e.
 // vec [5][T, H, d] fp32: u, a*u, r*w, w, k; sc [T, H, 2]: r.(a*u), r.k; v32 [T, H, d].
 template <typename T>
 __global__ void general_delta_prepare_kernel(float* __restrict__ vec, float* __restrict__ sc, float* __restrict__ v32,
                                              const T* __restrict__ proj, int proj_stride, const float* __restrict__ aw,
-                                             int aw_stride, const T* __restrict__ a_bias, const T* __restrict__ w2,
-                                             const T* __restrict__ w0, int n_tokens, int H, int d, int rank,
+                                             int aw_stride, const T* __restrict__ a_bias, const float* __restrict__ dec,
+                                             const T* __restrict__ w0, int n_tokens, int H, int d,
                                              float decay_floor) {
-  __shared__ float zs[GD_WARPS][GD_MAX_RANK];
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long item = (long)blockIdx.x * GD_WARPS + warp;
@@ -49,8 +58,6 @@ __global__ void general_delta_prepare_kernel(float* __restrict__ vec, float* __r
   const int n = H * d;
   const T* row = proj + (size_t)t * proj_stride;
   const float* awr = aw + (size_t)t * aw_stride;
-  for (int j = lane; j < rank; j += 32) zs[warp][j] = tanhf(awr[n + j]);
-  __syncwarp();
   float kk[GD_MAX_D / 32], ss = 0.f;
 #pragma unroll
   for (int i = 0; i < GD_MAX_D / 32; ++i) {
@@ -67,9 +74,7 @@ __global__ void general_delta_prepare_kernel(float* __restrict__ vec, float* __r
     const int c = lane + 32 * i;
     if (c < d) {
       const int col = h * d + c;
-      float z = to_f32<T>(w0[col]);
-      const T* w2r = w2 + (size_t)col * rank;
-      for (int j = 0; j < rank; ++j) z = fmaf(to_f32<T>(w2r[j]), zs[warp][j], z);
+      const float z = dec[(size_t)t * n + col] + to_f32<T>(w0[col]);
       const float decay = expf(-decay_floor / (1.0f + expf(-z)));
       const float rate = 1.0f / (1.0f + expf(-(awr[col] + to_f32<T>(a_bias[col]))));
       const float r = to_f32<T>(row[col]);
@@ -242,29 +247,43 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
   }
 }
 
-// o_out [T, H, d] fp32.  proj [T, >= 3 H d] (r, k, v) of type `dtype`; aw [T, H d + rank] fp32 (the removal rate's
-// projection, then the decay's inner projection); a_bias, w0 [H d] and w2 [H d, rank] of type `dtype`.
+// out [rows, cols] of type `dtype` = tanh(in), in fp32 with rows in_stride apart (the decay's inner projection).
+NHV_API int nhv_general_delta_tanh(int dtype, void* out, const float* in, int in_stride, int rows, int cols,
+                                   cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return 0;
+  NHV_REQUIRE(rows > 0 && cols > 0 && in_stride >= cols, "general_delta_tanh: bad sizes");
+  const size_t total = (size_t)rows * cols;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  if (dtype == NHV_F32)
+    nhv_launch(general_delta_tanh_kernel<float>, blocks, 256, 0, stream, (float*)out, in, in_stride, cols, total);
+  else if (dtype == NHV_BF16)
+    nhv_launch(general_delta_tanh_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, in, in_stride, cols, total);
+  else
+    NHV_REQUIRE(false, "general_delta_tanh: unknown dtype %d", dtype);
+  NHV_CHECK_LAUNCH("general_delta_tanh");
+  return 0;
+}
+
+// o_out [T, H, d] fp32.  proj [T, >= 3 H d] (r, k, v) of type `dtype`; aw [T, >= H d] fp32 (the removal rate's
+// projection); dec [T, H d] fp32 (the decay's projection W2 tanh(z)); a_bias, w0 [H d] of type `dtype`.
 // Scratch given by the caller, all fp32: vec [5][T, H, d]; sc [T, H, 2]; v32 [T, H, d].
 NHV_API int nhv_general_delta(int dtype, float* o_out, const void* proj, int proj_stride, const float* aw, int aw_stride,
-                              const void* a_bias, const void* w2, const void* w0, float* state, long state_stride,
+                              const void* a_bias, const float* dec, const void* w0, float* state, long state_stride,
                               float* vec, float* sc, float* v32, const int* cu_q, const int* q_start, const int* slots,
-                              int n_seqs, int n_tokens, int H, int d, int rank, float decay_floor,
-                              cudaStream_t stream) {
+                              int n_seqs, int n_tokens, int H, int d, float decay_floor, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(H > 0 && d > 0 && d <= GD_MAX_D, "general_delta: a head of %d channels is beyond the supported %d", d, GD_MAX_D);
-  NHV_REQUIRE(rank > 0 && rank <= GD_MAX_RANK, "general_delta: a decay projection of rank %d is beyond the supported %d", rank, GD_MAX_RANK);
-  NHV_REQUIRE(proj_stride >= 3 * H * d && aw_stride >= H * d + rank, "general_delta: rows too short for r, k, v / the rate and the decay");
+  NHV_REQUIRE(proj_stride >= 3 * H * d && aw_stride >= H * d, "general_delta: rows too short for r, k, v / the rate");
   NHV_REQUIRE(state_stride >= (long)H * d * d, "general_delta: the state holds fewer than heads * d * d floats");
   const long items = (long)n_tokens * H;
   const int pblocks = (int)((items + GD_WARPS - 1) / GD_WARPS);
   if (dtype == NHV_F32)
     nhv_launch(general_delta_prepare_kernel<float>, pblocks, GD_WARPS * 32, 0, stream, vec, sc, v32, (const float*)proj,
-               proj_stride, aw, aw_stride, (const float*)a_bias, (const float*)w2, (const float*)w0, n_tokens, H, d, rank,
-               decay_floor);
+               proj_stride, aw, aw_stride, (const float*)a_bias, dec, (const float*)w0, n_tokens, H, d, decay_floor);
   else if (dtype == NHV_BF16)
     nhv_launch(general_delta_prepare_kernel<__nv_bfloat16>, pblocks, GD_WARPS * 32, 0, stream, vec, sc, v32,
-               (const __nv_bfloat16*)proj, proj_stride, aw, aw_stride, (const __nv_bfloat16*)a_bias,
-               (const __nv_bfloat16*)w2, (const __nv_bfloat16*)w0, n_tokens, H, d, rank, decay_floor);
+               (const __nv_bfloat16*)proj, proj_stride, aw, aw_stride, (const __nv_bfloat16*)a_bias, dec,
+               (const __nv_bfloat16*)w0, n_tokens, H, d, decay_floor);
   else
     NHV_REQUIRE(false, "general_delta: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("general_delta_prepare");

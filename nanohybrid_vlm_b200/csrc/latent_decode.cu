@@ -10,9 +10,9 @@
 // partial sums of a token and head, where the sink (exp(sink) in the denominator, once) joins.  The cutting depends
 // on the token's position and on `n_splits` only.
 //
-// Block: 4 warps.  Q.K^T: warp w owns keys 16 w .. 16 w + 15 of a tile, all 16 heads, the row's elements in steps of
-// 16.  The running maximum is shared through shared memory; P goes to shared memory as bfloat16; P.V: warp w owns a
-// quarter of the latent's columns (NT tiles of 8), all 64 keys.  Tiles arrive by cp.async, the next while this one is
+// Block: 8 warps.  Q.K^T: warp w owns keys 8 w .. 8 w + 7 of a tile, all 16 heads, the row's elements in steps of 16
+// (even and odd steps in two chains of products).  The running maximum is shared through shared memory; P goes to
+// shared memory as bfloat16; P.V: warp w owns an eighth of the latent's columns (NT tiles of 8), all 64 keys.  Tiles arrive by cp.async, the next while this one is
 // worked on.  Shared-memory rows are round_up(row, 16) + 8 elements, an odd number of 16-byte chunks, so that ldmatrix
 // meets no bank conflicts; what no copy writes stays zero.
 #include <cuda_bf16.h>
@@ -23,7 +23,8 @@
 typedef __nv_bfloat16 bf16;
 
 constexpr int LD_BN = 64;            // keys per tile
-constexpr int LD_THREADS = 128;
+constexpr int LD_THREADS = 256;
+constexpr int LD_WARPS = LD_THREADS / 32;
 constexpr int LD_PS = LD_BN + 8;     // a row of P in shared memory
 constexpr float LD_LOG2E = 1.4426950408889634f;
 
@@ -50,7 +51,7 @@ __device__ __forceinline__ uint32_t ld_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// NT: tiles of 8 latent columns per warp (an even number; 4 NT 8 >= rank).
+// NT: tiles of 8 latent columns per warp (an even number; 8 NT 8 >= rank).
 template <int NT>
 __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q, int q_stride,
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   bf16* Qs = reinterpret_cast<bf16*>(ld_smem);          // [16][RS]
   bf16* Ks = Qs + 16 * RS;                              // [2][64][RS]
   bf16* Ps = Ks + 2 * LD_BN * RS;                       // [16][LD_PS]
-  float* red = reinterpret_cast<float*>(Ps + 16 * LD_PS);   // [4][16]
+  float* red = reinterpret_cast<float*>(Ps + 16 * LD_PS);   // [8][16]
 
   // the request of this token and the token's position
   int seq = 0;
@@ -92,11 +93,16 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   const int* table = block_table + (size_t)seq * bt_stride;
   auto fetch = [&](int tile, int stage) {
     bf16* dst = Ks + (size_t)stage * LD_BN * RS;
-    for (int kk = warp; kk < LD_BN; kk += 4) {
-      const int j = tile * LD_BN + kk;
+    int mine = -1;                                      // lane i < 8 looks up the page of key warp + 8 i
+    {
+      const int j = tile * LD_BN + warp + LD_WARPS * (lane & 7);
+      if (j <= pos) mine = table[j / page_size];
+    }
+#pragma unroll
+    for (int i = 0; i < LD_BN / LD_WARPS; ++i) {
+      const int kk = warp + LD_WARPS * i, j = tile * LD_BN + kk;
       bf16* d = dst + kk * RS;
-      int page = -1;
-      if (j <= pos) page = table[j / page_size];
+      const int page = __shfl_sync(0xffffffffu, mine, i);
       if (page >= 0 && page < n_pages) {
         const bf16* src = pages + ((size_t)page * page_size + j % page_size) * row;
         for (int c = lane; c < cpr; c += 32) ld_cp_async16(d + 8 * c, src + 8 * c);
@@ -106,7 +112,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
     }
   };
   fetch(tile0, 0);
-  for (int r = warp; r < 16; r += 4)                    // the queries of 16 heads
+  for (int r = warp; r < 16; r += LD_WARPS)             // the queries of 16 heads
     if (h0 + r < H) {
       const bf16* src = q + (size_t)tok * q_stride + (size_t)(h0 + r) * row;
       for (int c = lane; c < cpr; c += 32) ld_cp_async16(Qs + r * RS + 8 * c, src + 8 * c);
@@ -118,7 +124,7 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // rows g and g + 8
   const float sc2 = scale * LD_LOG2E;
-  const int ntw = (((rank >> 3) + 3) / 4 + 1) & ~1;       // tiles of 8 columns per warp, even
+  const int ntw = (((rank >> 3) + LD_WARPS - 1) / LD_WARPS + 1) & ~1;   // tiles of 8 columns per warp, even
   const int col_base = warp * ntw * 8;
 
   for (int tile = tile0; tile < tile1; ++tile) {
@@ -128,28 +134,32 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
     if (tile + 1 < tile1) fetch(tile + 1, stage ^ 1);
     ld_cp_async_commit();
     const bf16* Kt = Ks + (size_t)stage * LD_BN * RS;
-    // scores of 16 heads x this warp's 16 keys
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // scores of 16 heads x this warp's 8 keys; one load of the keys serves two steps of 16 elements
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
+      float s2[4] = {0.f, 0.f, 0.f, 0.f};
       const bf16* qa = Qs + (lane & 15) * RS + (lane >> 4) * 8;
-      const bf16* kb = Kt + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * RS + ((lane >> 3) & 1) * 8;
-      for (int ks = 0; ks < ksteps; ++ks) {
+      const bf16* kb = Kt + (warp * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
+      for (int ks = 0; ks < ksteps; ks += 2) {
         uint32_t a[4], b[4];
+        ld_ldmatrix_x4(b, kb + ks * 16);                // behind an odd last step it reads on into memory that is not used
         ld_ldmatrix_x4(a, qa + ks * 16);
-        ld_ldmatrix_x4(b, kb + ks * 16);
-        ld_mma(s[0], a, b[0], b[1]);
-        ld_mma(s[1], a, b[2], b[3]);
+        ld_mma(s, a, b[0], b[1]);
+        if (ks + 1 < ksteps) {
+          ld_ldmatrix_x4(a, qa + ks * 16 + 16);
+          ld_mma(s2, a, b[2], b[3]);
+        }
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[e] += s2[e];
     }
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = tile * LD_BN + warp * 16 + nt * 8 + 2 * t4 + (e & 1);
-        s[nt][e] = j <= pos ? s[nt][e] * sc2 : -INFINITY;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
-      }
+    for (int e = 0; e < 4; ++e) {
+      const int j = tile * LD_BN + warp * 8 + 2 * t4 + (e & 1);
+      s[e] = j <= pos ? s[e] * sc2 : -INFINITY;
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[e]);
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -164,18 +174,19 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int rr = g + 8 * r;
-      const float m_new = fmaxf(fmaxf(m_run[r], fmaxf(red[rr], red[16 + rr])), fmaxf(red[32 + rr], red[48 + rr]));
+      float m_new = m_run[r];
+#pragma unroll
+      for (int w = 0; w < LD_WARPS; ++w) m_new = fmaxf(m_new, red[w * 16 + rr]);
       alpha[r] = exp2f(m_run[r] - m_new);               // the first tile has a key that is seen: m_new is finite
       m_run[r] = m_new;
       l_run[r] *= alpha[r];
     }
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const float p0 = exp2f(s[nt][0] - m_run[0]), p1 = exp2f(s[nt][1] - m_run[0]);
-      const float p2 = exp2f(s[nt][2] - m_run[1]), p3 = exp2f(s[nt][3] - m_run[1]);
+    {
+      const float p0 = exp2f(s[0] - m_run[0]), p1 = exp2f(s[1] - m_run[0]);
+      const float p2 = exp2f(s[2] - m_run[1]), p3 = exp2f(s[3] - m_run[1]);
       l_run[0] += p0 + p1;
       l_run[1] += p2 + p3;
-      const int c = warp * 16 + nt * 8 + 2 * t4;
+      const int c = warp * 8 + 2 * t4;
       *reinterpret_cast<uint32_t*>(Ps + g * LD_PS + c) = ld_pack(p0, p1);
       *reinterpret_cast<uint32_t*>(Ps + (g + 8) * LD_PS + c) = ld_pack(p2, p3);
     }
@@ -220,7 +231,10 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   __syncthreads();
   if (tid < 16 && h0 + tid < H) {
     const size_t at = (part + (size_t)(h0 + tid) * n_splits) * 2;
-    part_ml[at + 1] = red[tid] + red[16 + tid] + red[32 + tid] + red[48 + tid];
+    float l = 0.f;
+#pragma unroll
+    for (int w = 0; w < LD_WARPS; ++w) l += red[w * 16 + tid];
+    part_ml[at + 1] = l;
   }
   if (warp == 0 && t4 == 0) {                           // every thread holds the maxima of its two rows
 #pragma unroll
@@ -269,7 +283,7 @@ __global__ void latent_decode_merge_kernel(bf16* __restrict__ out, int out_strid
 
 NHV_API int nhv_latent_decode_supports(int H, int rank, int row) {
   const int RS = (row + 15) / 16 * 16 + 8;
-  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + 64 * sizeof(float);
+  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + LD_WARPS * 16 * sizeof(float);
   return H > 0 && rank > 0 && rank % 8 == 0 && row % 8 == 0 && row >= rank && rank <= 512 && smem <= 227 * 1024;
 }
 
@@ -284,7 +298,7 @@ NHV_API int nhv_latent_decode(void* out, int out_stride, const void* q, int q_st
   NHV_REQUIRE(n_splits > 0 && page_size > 0 && n_pages > 0 && bt_stride > 0 && q_stride % 8 == 0 &&
               ((uintptr_t)q & 15) == 0 && ((uintptr_t)pages & 15) == 0, "latent_decode: bad geometry or alignment");
   const int RS = (row + 15) / 16 * 16 + 8;
-  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + 64 * sizeof(float);
+  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + LD_WARPS * 16 * sizeof(float);
   dim3 grid(n_splits, n_tokens, (H + 15) / 16);
 #define LAUNCH(NT)                                                                                                   \
   do {                                                                                                               \
@@ -295,10 +309,10 @@ NHV_API int nhv_latent_decode(void* out, int out_stride, const void* q, int q_st
                (const bf16*)pages, block_table, bt_stride, cu_q, kv_len, n_seqs, H, rank, row, page_size, n_pages,   \
                scale);                                                                                               \
   } while (0)
-  const int ntw = (((rank >> 3) + 3) / 4 + 1) & ~1;
-  if (ntw <= 4) LAUNCH(4);
-  else if (ntw <= 8) LAUNCH(8);
-  else LAUNCH(16);
+  const int ntw = (((rank >> 3) + LD_WARPS - 1) / LD_WARPS + 1) & ~1;
+  if (ntw <= 2) LAUNCH(2);
+  else if (ntw <= 4) LAUNCH(4);
+  else LAUNCH(8);
 #undef LAUNCH
   NHV_CHECK_LAUNCH("latent_decode");
   nhv_launch(latent_decode_merge_kernel, dim3(n_tokens * H), dim3(128), 0, stream, (bf16*)out, out_stride,

@@ -61,7 +61,8 @@ _SIGNATURES = {
     "nhv_causal_filter_add": [I, P, P, I, P, I, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
     "nhv_latent_rope_store": [I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "nhv_gemm_nt_simt_batched": [I, P, P, P, I, I, I, I, I, I, I, I, ctypes.c_long, ctypes.c_long, ctypes.c_long, P],
-    "nhv_general_delta": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, I, I, I, I, I, F, P],
+    "nhv_general_delta": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, I, I, I, I, F, P],
+    "nhv_general_delta_tanh": [I, P, P, I, I, I, P],
     "nhv_sigmoid_mul_heads": [I, P, I, P, I, P, I, I, I, I, I, P],
     "nhv_latent_gather": [I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
     "nhv_latent_assemble": [I, P, P, P, P, P, I, P, I, ctypes.c_long, I, I, I, I, I, I, I, P],

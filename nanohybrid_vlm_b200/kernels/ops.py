@@ -322,14 +322,15 @@ def linear_heads(out, x, weight) -> None:
          K, out.stride(0), 0, H, x.stride(1), N * K, out.stride(1), stream_ptr())
 
 
-LINEAR_HEADS_SIMT_ROWS = 1 << 30    # tokens up to which the per-head products in bfloat16 run on the CUDA cores
+LINEAR_HEADS_SIMT_ROWS = 0          # tokens up to which the per-head products in bfloat16 run on the CUDA cores
 
 
 def general_delta(o, proj, aw, a_bias, w2, w0, state, batch, H: int, d: int, decay_floor: float) -> None:
     """The generalised delta rule over the step's tokens.  proj [T, >= 3 H d] (r, k, v in the storage type), aw
     [T, H d + rank] float32 (the removal rate's projection, then the decay's inner projection), a_bias / w0 [H d] and
     w2 [H d, rank] in the storage type, state [slots, H d d] float32 -> o [T, H d] float32 (before its norm and gate).
-    The decay per key channel is exp(-decay_floor * sigmoid(w2 tanh(inner) + w0))."""
+    The decay per key channel is exp(-decay_floor * sigmoid(w2 tanh(inner) + w0)); tanh(inner) takes the storage type
+    as the operand of the product with w2, whose sums are float32."""
     _need_cuda(o, proj, aw, a_bias, w2, w0, state)
     T, n = proj.shape[0], H * d
     rank = w2.shape[1]
@@ -337,11 +338,17 @@ def general_delta(o, proj, aw, a_bias, w2, w0, state, batch, H: int, d: int, dec
     assert aw.shape == (T, n + rank) and o.dtype == state.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, n)
     assert a_bias.dtype == w2.dtype == w0.dtype == proj.dtype and w2.is_contiguous() and w2.shape == (n, rank)
     assert a_bias.numel() == n and w0.numel() == n and state.stride(1) == 1
+    # the decay's second projection as a product of its own: tanh of the inner projection in the storage type, 32-bit sums
+    inner = torch.empty(T, rank, dtype=proj.dtype, device=proj.device)
+    call("nhv_general_delta_tanh", dtype_code(proj), inner.data_ptr(), aw.data_ptr() + 4 * n, aw.stride(0), T, rank,
+         stream_ptr())
+    dec = torch.empty(T, n, dtype=torch.float32, device=proj.device)
+    linear_f32(dec, inner, w2)
     scratch = torch.empty(T * (6 * n + 2 * H), dtype=torch.float32, device=proj.device)
     vec, v32, sc = scratch.data_ptr(), scratch.data_ptr() + 4 * 5 * T * n, scratch.data_ptr() + 4 * 6 * T * n
     call("nhv_general_delta", dtype_code(proj), o.data_ptr(), proj.data_ptr(), proj.stride(0), aw.data_ptr(), aw.stride(0),
-         a_bias.data_ptr(), w2.data_ptr(), w0.data_ptr(), state.data_ptr(), state.stride(0), vec, sc, v32,
-         batch.cu_q.data_ptr(), batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, d, rank,
+         a_bias.data_ptr(), dec.data_ptr(), w0.data_ptr(), state.data_ptr(), state.stride(0), vec, sc, v32,
+         batch.cu_q.data_ptr(), batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, d,
          float(decay_floor), stream_ptr())
 
 
