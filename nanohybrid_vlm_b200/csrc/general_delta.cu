@@ -201,9 +201,12 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
     const float* vs_u = smem + stage * STAGE;
     const float* vs_v = vs_u + 5 * GD_CHUNK * DP;
     const float* vs_s = vs_v + GD_CHUNK * GD_COLS;
+    // the sums over a lane's rows run as two chains each (even and odd rows), fixed whatever the step's shape; the
+    // loop is unrolled so that the next tokens' vectors are on their way while this token's sums cross the lanes
+#pragma unroll(R <= 8 ? 4 : (R <= 16 ? 2 : 1))
     for (int tt = 0; tt < cn; ++tt) {
       const float* base = vs_u + tt * DP + 4 * part;
-      float A = 0.f, B = 0.f;
+      float A = 0.f, B = 0.f, A2 = 0.f, B2 = 0.f;
       float4 w4[R / 4], au4[R / 4], k4[R / 4];
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
@@ -212,11 +215,13 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(
         au4[j] = *reinterpret_cast<const float4*>(base + GD_CHUNK * DP + 4 * GD_LANES * j);
         w4[j] = *reinterpret_cast<const float4*>(base + 3 * GD_CHUNK * DP + 4 * GD_LANES * j);
         k4[j] = *reinterpret_cast<const float4*>(base + 4 * GD_CHUNK * DP + 4 * GD_LANES * j);
-        A = fmaf(u.x, S[4 * j], A);      B = fmaf(rw.x, S[4 * j], B);
-        A = fmaf(u.y, S[4 * j + 1], A);  B = fmaf(rw.y, S[4 * j + 1], B);
-        A = fmaf(u.z, S[4 * j + 2], A);  B = fmaf(rw.z, S[4 * j + 2], B);
-        A = fmaf(u.w, S[4 * j + 3], A);  B = fmaf(rw.w, S[4 * j + 3], B);
+        A = fmaf(u.x, S[4 * j], A);        B = fmaf(rw.x, S[4 * j], B);
+        A2 = fmaf(u.y, S[4 * j + 1], A2);  B2 = fmaf(rw.y, S[4 * j + 1], B2);
+        A = fmaf(u.z, S[4 * j + 2], A);    B = fmaf(rw.z, S[4 * j + 2], B);
+        A2 = fmaf(u.w, S[4 * j + 3], A2);  B2 = fmaf(rw.w, S[4 * j + 3], B2);
       }
+      A += A2;
+      B += B2;
 #pragma unroll
       for (int off = 1; off < GD_LANES; off <<= 1) {
         A += __shfl_xor_sync(0xffffffffu, A, off);

@@ -420,7 +420,7 @@ def latent_attention(out, q_lat, pages, tables, batch, H: int, rank: int, row: i
     assert q_lat.shape == (T, H * row) and out.shape == (T, H * rank) and out.dtype == pages.dtype == torch.bfloat16
     assert q_lat.stride(1) == 1 and out.stride(1) == 1 and sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == H)
     tiles = -(-batch.max_kv_len // 64)
-    pieces = max(1, min(tiles, 64, -(-2 * 148 // (T * -(-H // 16)))))
+    pieces = max(1, min(tiles, 64, 2 * 148 // (T * -(-H // 16))))      # two rounds of blocks over the 148 SMs at most
     part = torch.empty(T * H * pieces * (rank + 2), dtype=torch.float32, device=out.device)
     call("nhv_latent_decode", out.data_ptr(), out.stride(0), q_lat.data_ptr(), q_lat.stride(0), pages.data_ptr(),
          tables.block_tables.data_ptr(), tables.block_tables.stride(0), batch.cu_q.data_ptr(), batch.kv_len.data_ptr(),
