@@ -736,7 +736,7 @@ def bench_designs(args) -> dict:
              "sigmoid_mul": "act_mul", "add_row_bias": "act_mul", "clamped_glu": "act_mul", "moe_route": "router",
              "moe_experts": "experts", "moe_combine": "experts_sum", "causal_filter_add": "short_conv",
              "latent_rope_store": "rope_store", "linear_heads": "gemm_heads", "attention_sink_simt": "attention",
-             "latent_attention": "attention", "general_delta": "delta_rule", "sigmoid_mul_heads": "act_mul",
+             "latent_attention": "attention", "latent_expand": "attention", "general_delta": "delta_rule", "sigmoid_mul_heads": "act_mul",
              "relu_squared": "act_mul", "scale_softcap": "act_mul"}
     kinds = {k: v for k, v in kinds.items() if hasattr(ops, k)}
     stock = {name: getattr(ops, name) for name in kinds}

@@ -162,6 +162,8 @@ struct alignas(64) Params {
   const int* cu_q;
   const int* kv_len;
   const float* sinks;     // per query head, or null: exp(sink) joins the softmax denominator (no key, no value, no scale)
+  const float* slopes;    // per query head, or null: the score loses slopes[head] times the distance between query and key
+  float inv_scale;        // 1 / scale: the distance term joins the raw score, which the exponent's multiply-add scales
   int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, chunk, tokens_per_block;
   float scale_log2;
 };
@@ -340,6 +342,8 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     const int all_lo = nhv_first_key(pos_hi, p.window, p.chunk);
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     float m_run = -INFINITY, l = 0.f;
+    // slope per position of distance, in units of the raw score (0: no distance term)
+    const float slope = (p.slopes && valid) ? p.slopes[kvh * G + g] * p.inv_scale : 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int key_base = key_begin + j * BN;
@@ -354,6 +358,12 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
       // and the scaling folded into the exponent's multiply-add.  A tile that some row of the block sees only
       // in part takes the masked path.
       const bool masked = !(key_base >= all_lo && key_base + BN - 1 <= all_hi);
+      if (p.slopes) {                                           // score - slope * (row - key), before maximum and mask
+        const float at0 = slope * (float)(key_base - row_hi);
+#pragma unroll
+        for (int i = 0; i < BN; ++i)
+          sr[i >> 5][i & 31] = __float_as_uint(__uint_as_float(sr[i >> 5][i & 31]) + fmaf(slope, (float)i, at0));
+      }
       if (masked) {
 #pragma unroll
         for (int i = 0; i < BN; ++i) {
@@ -512,7 +522,7 @@ NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, i
                                        const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                                        int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int nq, int nkv,
                                        int page_size, int n_pages, int window, int chunk, float scale, const float* sinks,
-                                       cudaStream_t stream) {
+                                       const float* slopes, cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   const int G = nq / nkv;
   ATT_REQUIRE(G <= BM, "attention: a group of %d query heads is beyond the %d rows of a block", G, BM);
@@ -543,6 +553,9 @@ NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, i
   p.cu_q = cu_q;
   p.kv_len = kv_len;
   p.sinks = sinks;
+  p.slopes = slopes;
+  p.inv_scale = 1.0f / scale;
+  ATT_REQUIRE(slopes == nullptr || scale > 0.f, "attention (tcgen05): a distance term needs a positive scale");
   p.q_stride = q_stride;
   p.out_stride = out_stride;
   p.bt_stride = bt_stride;

@@ -891,8 +891,8 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     neither takes runs in the mma.sync kernel, whose single-token path shares a request's tiles between
     blocks and merges them (scratch: one partial result per piece of a request and head block).
     ``sinks`` [nq] float32: exp(sink) joins each head's softmax denominator once (where the head's sum is final).
-    ``slopes`` [nq] float32: head h's score loses slopes[h] times the distance between query and key; such layers run in
-    the mma.sync kernel, prompt portions and single tokens alike."""
+    ``slopes`` [nq] float32: head h's score loses slopes[h] times the distance between query and key; the tcgen05 and
+    the mma.sync kernels take them, the TMA kernel for single tokens does not, so those run in the mma.sync kernel."""
     _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks, slopes)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq and sinks.is_contiguous())
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == nq and slopes.is_contiguous())
@@ -902,14 +902,14 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     assert two == 2 and h == nkv and d == head_dim
     assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
     launch, tile = attention_mma.get(head_dim)[:2]
-    if (n_prefill_tokens > 0 and slopes is None and USE_TCGEN05_ATTENTION
+    if (n_prefill_tokens > 0 and USE_TCGEN05_ATTENTION and (slopes is None or scale > 0)
             and attention_tcgen05.supports(head_dim, nq, nkv, page_size)):
         # prompt portions on the 5th-generation tensor cores; single tokens stay with the split kernel below
         library.LAUNCHES += 1
         attention_tcgen05.get(head_dim)[0](
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
-            nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks), stream_ptr())
+            nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks), _ptr(slopes), stream_ptr())
         if n_decode_seqs == 0:
             return
         n_prefill_tokens = n_prefill_seqs = 0
