@@ -10,9 +10,10 @@
 // partial sums of a token and head, where the sink (exp(sink) in the denominator, once) joins.  The cutting depends
 // on the token's position and on `n_splits` only.
 //
-// Block: 8 warps.  Q.K^T: warp w owns keys 8 w .. 8 w + 7 of a tile, all 16 heads, the row's elements in steps of 16
-// (even and odd steps in two chains of products).  The running maximum is shared through shared memory; P goes to
-// shared memory as bfloat16; P.V: warp w owns an eighth of the latent's columns (NT tiles of 8), all 64 keys.  Tiles arrive by cp.async, the next while this one is
+// Block: 16 warps.  Q.K^T: warps w and w + 8 own keys 8 w .. 8 w + 7 of a tile, all 16 heads, each one half of the
+// row's elements in steps of 16 (even and odd steps in two chains of products); the upper warp hands its partial
+// scores to the lower one through shared memory.  The running maximum is shared through shared memory; P goes to
+// shared memory as bfloat16; P.V: warp w owns a sixteenth of the latent's columns (NT tiles of 8), all 64 keys.  Tiles arrive by cp.async, the next while this one is
 // worked on.  Shared-memory rows are round_up(row, 16) + 8 elements, an odd number of 16-byte chunks, so that ldmatrix
 // meets no bank conflicts; what no copy writes stays zero.
 #include <cuda_bf16.h>
@@ -23,8 +24,9 @@
 typedef __nv_bfloat16 bf16;
 
 constexpr int LD_BN = 64;            // keys per tile
-constexpr int LD_THREADS = 256;
+constexpr int LD_THREADS = 512;
 constexpr int LD_WARPS = LD_THREADS / 32;
+constexpr int LD_KG = LD_BN / 8;       // groups of 8 keys in a tile
 constexpr int LD_PS = LD_BN + 8;     // a row of P in shared memory
 constexpr float LD_LOG2E = 1.4426950408889634f;
 
@@ -51,9 +53,9 @@ __device__ __forceinline__ uint32_t ld_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// NT: tiles of 8 latent columns per warp (an even number; 8 NT 8 >= rank).
+// NT: tiles of 8 latent columns per warp (an even number; 16 NT 8 >= rank).
 template <int NT>
-__global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
+__global__ void __launch_bounds__(LD_THREADS, 1) latent_decode_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q, int q_stride,
     const bf16* __restrict__ pages, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
     const int* __restrict__ kv_len, int n_seqs, int H, int rank, int row, int page_size, int n_pages, float scale) {
@@ -66,7 +68,8 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   bf16* Qs = reinterpret_cast<bf16*>(ld_smem);          // [16][RS]
   bf16* Ks = Qs + 16 * RS;                              // [2][64][RS]
   bf16* Ps = Ks + 2 * LD_BN * RS;                       // [16][LD_PS]
-  float* red = reinterpret_cast<float*>(Ps + 16 * LD_PS);   // [8][16]
+  float* red = reinterpret_cast<float*>(Ps + 16 * LD_PS);   // [16][16]
+  float4* sred = reinterpret_cast<float4*>(red + LD_WARPS * 16);   // [8][32]: partial scores of the upper warps
 
   // the request of this token and the token's position
   int seq = 0;
@@ -93,9 +96,9 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   const int* table = block_table + (size_t)seq * bt_stride;
   auto fetch = [&](int tile, int stage) {
     bf16* dst = Ks + (size_t)stage * LD_BN * RS;
-    int mine = -1;                                      // lane i < 8 looks up the page of key warp + 8 i
+    int mine = -1;                                      // lane i looks up the page of key warp + 16 i
     {
-      const int j = tile * LD_BN + warp + LD_WARPS * (lane & 7);
+      const int j = tile * LD_BN + warp + LD_WARPS * (lane % (LD_BN / LD_WARPS));
       if (j <= pos) mine = table[j / page_size];
     }
 #pragma unroll
@@ -125,6 +128,9 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // rows g and g + 8
   const float sc2 = scale * LD_LOG2E;
   const int ntw = (((rank >> 3) + LD_WARPS - 1) / LD_WARPS + 1) & ~1;   // tiles of 8 columns per warp, even
+  const int kg = warp & (LD_KG - 1);                    // this warp's group of 8 keys in Q.K^T
+  const bool upper = warp >= LD_KG;                     // the warp with the upper half of the row's steps
+  const int ksplit = (ksteps + 3) / 4 * 2;              // an even number of steps for the lower warp
   const int col_base = warp * ntw * 8;
 
   for (int tile = tile0; tile < tile1; ++tile) {
@@ -134,13 +140,14 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
     if (tile + 1 < tile1) fetch(tile + 1, stage ^ 1);
     ld_cp_async_commit();
     const bf16* Kt = Ks + (size_t)stage * LD_BN * RS;
-    // scores of 16 heads x this warp's 8 keys; one load of the keys serves two steps of 16 elements
+    // scores of 16 heads x this warp's 8 keys over its half of the steps; one load of the keys serves two steps
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
       float s2[4] = {0.f, 0.f, 0.f, 0.f};
       const bf16* qa = Qs + (lane & 15) * RS + (lane >> 4) * 8;
-      const bf16* kb = Kt + (warp * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
-      for (int ks = 0; ks < ksteps; ks += 2) {
+      const bf16* kb = Kt + (kg * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
+      const int ks0 = upper ? ksplit : 0, ks1 = upper ? ksteps : min(ksplit, ksteps);
+      for (int ks = ks0; ks < ks1; ks += 2) {
         uint32_t a[4], b[4];
         ld_ldmatrix_x4(b, kb + ks * 16);                // behind an odd last step it reads on into memory that is not used
         ld_ldmatrix_x4(a, qa + ks * 16);
@@ -153,21 +160,27 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[e] += s2[e];
     }
+    if (upper) sred[kg * 32 + lane] = make_float4(s[0], s[1], s[2], s[3]);
+    __syncthreads();
     float mx[2] = {-INFINITY, -INFINITY};
+    if (!upper) {
+      const float4 other = sred[kg * 32 + lane];
+      s[0] += other.x; s[1] += other.y; s[2] += other.z; s[3] += other.w;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = tile * LD_BN + warp * 8 + 2 * t4 + (e & 1);
-      s[e] = j <= pos ? s[e] * sc2 : -INFINITY;
-      mx[e >> 1] = fmaxf(mx[e >> 1], s[e]);
+      for (int e = 0; e < 4; ++e) {
+        const int j = tile * LD_BN + kg * 8 + 2 * t4 + (e & 1);
+        s[e] = j <= pos ? s[e] * sc2 : -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[e]);
+      }
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     }
-    if (t4 == 0) {
-      red[warp * 16 + g] = mx[0];
-      red[warp * 16 + g + 8] = mx[1];
+    if (t4 == 0 && !upper) {
+      red[kg * 16 + g] = mx[0];
+      red[kg * 16 + g + 8] = mx[1];
     }
     __syncthreads();
     float alpha[2];
@@ -176,17 +189,17 @@ __global__ void __launch_bounds__(LD_THREADS) latent_decode_kernel(
       const int rr = g + 8 * r;
       float m_new = m_run[r];
 #pragma unroll
-      for (int w = 0; w < LD_WARPS; ++w) m_new = fmaxf(m_new, red[w * 16 + rr]);
+      for (int w = 0; w < LD_KG; ++w) m_new = fmaxf(m_new, red[w * 16 + rr]);
       alpha[r] = exp2f(m_run[r] - m_new);               // the first tile has a key that is seen: m_new is finite
       m_run[r] = m_new;
       l_run[r] *= alpha[r];
     }
-    {
+    if (!upper) {
       const float p0 = exp2f(s[0] - m_run[0]), p1 = exp2f(s[1] - m_run[0]);
       const float p2 = exp2f(s[2] - m_run[1]), p3 = exp2f(s[3] - m_run[1]);
       l_run[0] += p0 + p1;
       l_run[1] += p2 + p3;
-      const int c = warp * 8 + 2 * t4;
+      const int c = kg * 8 + 2 * t4;
       *reinterpret_cast<uint32_t*>(Ps + g * LD_PS + c) = ld_pack(p0, p1);
       *reinterpret_cast<uint32_t*>(Ps + (g + 8) * LD_PS + c) = ld_pack(p2, p3);
     }
@@ -283,7 +296,7 @@ __global__ void latent_decode_merge_kernel(bf16* __restrict__ out, int out_strid
 
 NHV_API int nhv_latent_decode_supports(int H, int rank, int row) {
   const int RS = (row + 15) / 16 * 16 + 8;
-  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + LD_WARPS * 16 * sizeof(float);
+  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + (LD_WARPS * 16 + LD_KG * 32 * 4) * sizeof(float);
   return H > 0 && rank > 0 && rank % 8 == 0 && row % 8 == 0 && row >= rank && rank <= 512 && smem <= 227 * 1024;
 }
 
@@ -298,7 +311,7 @@ NHV_API int nhv_latent_decode(void* out, int out_stride, const void* q, int q_st
   NHV_REQUIRE(n_splits > 0 && page_size > 0 && n_pages > 0 && bt_stride > 0 && q_stride % 8 == 0 &&
               ((uintptr_t)q & 15) == 0 && ((uintptr_t)pages & 15) == 0, "latent_decode: bad geometry or alignment");
   const int RS = (row + 15) / 16 * 16 + 8;
-  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + LD_WARPS * 16 * sizeof(float);
+  const size_t smem = (size_t)((16 + 2 * LD_BN) * RS + 16 * LD_PS) * sizeof(bf16) + (LD_WARPS * 16 + LD_KG * 32 * 4) * sizeof(float);
   dim3 grid(n_splits, n_tokens, (H + 15) / 16);
 #define LAUNCH(NT)                                                                                                   \
   do {                                                                                                               \
@@ -311,8 +324,7 @@ NHV_API int nhv_latent_decode(void* out, int out_stride, const void* q, int q_st
   } while (0)
   const int ntw = (((rank >> 3) + LD_WARPS - 1) / LD_WARPS + 1) & ~1;
   if (ntw <= 2) LAUNCH(2);
-  else if (ntw <= 4) LAUNCH(4);
-  else LAUNCH(8);
+  else LAUNCH(4);
 #undef LAUNCH
   NHV_CHECK_LAUNCH("latent_decode");
   nhv_launch(latent_decode_merge_kernel, dim3(n_tokens * H), dim3(128), 0, stream, (bf16*)out, out_stride,
