@@ -34,6 +34,7 @@ from .page_pool import OutOfPages, PagePool, StateSlotAllocator
 class GroupSpec:
     window: int | None      # None: keep every key
     chunk: int | None = None    # n: only keys at or after the start of the newest token's chunk of n positions are read
+    keep_first: int = 0         # with a window: the keys of the first keep_first positions are never given back
 
     @property
     def gives_back(self) -> bool:
@@ -44,7 +45,7 @@ class GroupSpec:
 @dataclass
 class _Request:
     tables: list[list[int]]                 # per group: physical page per logical page (-1: given back)
-    released: list[int]                     # per group: logical pages [0, released) were given back
+    released: list[int]                     # per group: logical pages [kept first pages, released) were given back
     state_slot: int | None = None
     num_tokens: int = 0                     # tokens that have pages
     serial: int = 0                         # a number no other request record of this manager ever had
@@ -261,10 +262,11 @@ class CacheManager:
         freed = 0
         for g in range(len(self.groups)):
             first = min(self._first_needed_page(g, num_computed), len(req.tables[g]))
-            if first > req.released[g]:
-                pages = [p for p in req.tables[g][req.released[g]:first] if p >= 0]
+            start = max(req.released[g], -(-self.groups[g].keep_first // self.page_size))   # kept first pages stay
+            if first > start:
+                pages = [p for p in req.tables[g][start:first] if p >= 0]
                 self.pools[g].free(pages)
-                for i in range(req.released[g], first):
+                for i in range(start, first):
                     req.tables[g][i] = -1
                 req.released[g] = first
                 freed += len(pages)

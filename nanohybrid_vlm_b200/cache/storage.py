@@ -38,7 +38,7 @@ class CacheLayout:
             mine: list[int | None] = []
             for leaf in leaves(need):
                 if isinstance(leaf, PagedKVNeed):
-                    g = GroupSpec(leaf.window, leaf.chunk)
+                    g = GroupSpec(leaf.window, leaf.chunk, leaf.keep_first if leaf.window is not None else 0)
                     if g not in groups:
                         groups.append(g)
                     mine.append(groups.index(g))

@@ -25,6 +25,8 @@
 // Two more: a bias by distance, score - slopes[head] * (query position - key position), and pages with one plane
 // (planes == 1): a row of such a page is the key, and its leading dv elements are the value as well (keys and
 // values that are one latent vector per token, stored once).
+// And kept first keys (keep_first, with a window): a query also sees the keys at positions below keep_first, at their
+// true positions; their chunks are visited before the window's.
 #include <math.h>
 
 #include "nhv_common.cuh"
@@ -41,7 +43,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
                                        int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                        int n_seqs, int nq, int nkv, int d, int page_size, int n_pages, int window,
                                        float scale, int TQ, int GS, int dv, int row, const float* __restrict__ sinks,
-                                       int chunk, const float* __restrict__ slopes, int planes) {
+                                       int chunk, const float* __restrict__ slopes, int planes, int keep_first) {
   extern __shared__ float smem[];
   constexpr int AT_COLS = COLS, AT_PAIRS_PER_WARP = AT_ACC / COLS, AT_MAX_PAIRS = AT_PAIRS_PER_WARP * AT_WARPS;
   pdl_prologue();
@@ -102,8 +104,11 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
   int first_key = 0;
   first_key = nhv_first_key(pos_lo, window, chunk);
   const int c_begin = (first_key / AT_CHUNK) * AT_CHUNK;
+  // kept first keys: the chunks that hold keys [0, keep_first) come before the window's own chunks
+  const int kept_end = keep_first > 0 ? min(((keep_first + AT_CHUNK - 1) / AT_CHUNK) * AT_CHUNK, c_begin) : 0;
 
-  for (int c0 = c_begin; c0 <= pos_hi; c0 += AT_CHUNK) {
+  for (int c0 = kept_end > 0 ? 0 : c_begin; c0 <= pos_hi; c0 += AT_CHUNK) {
+    if (c0 >= kept_end && c0 < c_begin) c0 = c_begin;
     __syncthreads();
     // Stage 32 keys and values (zero where there is no key or its page was given back).
     if (threadIdx.x < AT_CHUNK) {
@@ -140,10 +145,10 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
       const int tq = p / gs;
       const int pos = pos_lo + tq;
       const int lo = nhv_first_key(pos, window, chunk);
-      if (c0 > pos || c0 + AT_CHUNK <= lo) continue;  // no key of this chunk is visible to this query
+      if (c0 > pos || (c0 + AT_CHUNK <= lo && c0 >= keep_first)) continue;  // no key of this chunk is visible to this query
       const int j = c0 + lane;
       float s = -INFINITY;
-      if (j <= pos && j >= lo && key_ok[lane]) {
+      if (j <= pos && (j >= lo || j < keep_first) && key_ok[lane]) {
         const float* qv = Qs + p * d;
         const float* kv = Ks + lane * ks;
         float acc = 0.f;
@@ -195,8 +200,9 @@ NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* 
                                   const void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
                                   const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int dv, int row,
                                   int page_size, int n_pages, int window, int chunk, float scale, const float* sinks,
-                                  const float* slopes, int planes, cudaStream_t stream) {
+                                  const float* slopes, int planes, int keep_first, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
+  NHV_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention: kept first keys go with a window");
   NHV_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   NHV_REQUIRE(d > 0 && d <= AT_MAX_D && dv > 0 && dv <= AT_MAX_D, "attention: head sizes %d / %d are beyond the supported %d",
               d, dv, AT_MAX_D);
@@ -220,7 +226,8 @@ NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* 
                                     (int)smem), "attention");                                                        \
     nhv_launch(attn_paged_simt_kernel<T, COLS>, grid, AT_WARPS * 32, smem, stream,                                   \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,        \
-        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk, slopes, planes);       \
+        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk, slopes, planes,        \
+        keep_first);                                                                                                 \
   } while (0)
 #define LAUNCH_COLS(T)                 \
   do {                                 \
@@ -243,5 +250,5 @@ NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out
                                const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int page_size,
                                int n_pages, int window, float scale, cudaStream_t stream) {
   return nhv_attention_simt_ex(dtype, q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len,
-                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, 0, scale, nullptr, nullptr, 2, stream);
+                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, 0, scale, nullptr, nullptr, 2, 0, stream);
 }

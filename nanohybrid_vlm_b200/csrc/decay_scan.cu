@@ -1,0 +1,194 @@
+// Linear recurrences with a matrix state per head that decays per key channel, for packed steps of several requests:
+//
+//   S_t = diag(w_t) S_(t-1) + k_t v_t^T                      S [dk, dv] per head, fp32, one per live request
+//   read before the update (a bonus b for the current token):  o_t = (S_(t-1) + diag(b) k_t v_t^T)^T r_t
+//   read after the update:                                     o_t = S_t^T r_t
+//
+// Both reads are  o_t[v] = sum_k r'_k S_(t-1)[k, v] + c_t v_t[v]  with r' = r and c_t = sum_k r_k b_k k_k in the first
+// form, r' = r * w_t and c_t = r_t . k_t in the second; r' and c_t are made once per token while it is staged, so the
+// loop over the state has one multiply-add for the read and one for the update per element.
+// The decay is a tensor per token and key channel (fp32, [T, H dk]) or one constant per head.  r, k and v come in the
+// storage type (the projections' output), optionally through SiLU, and are widened once; everything else is fp32.
+//
+// decay_lowrank: w[t, c] = exp(-exp(w0[c] + sum_j tanh(inner[t, j]) w2[c, j])), the decay of the first form from the
+// fp32 sums of its inner projection; the tanh stays fp32 and the small second product is summed in fp32 in a fixed order.
+//
+// Block = (request, head, 16 columns of the state); a column lives in 8 lanes, lane l holding the key channels
+// 32 i + 4 l .. + 3 of it in registers (KPL channels per lane).  Tokens are staged 16 at a time in shared memory (8 for the widest heads).
+// State layout per slot: [H][dv][dk].  A request with q_start == 0 starts from zeros whatever its slot held; a request
+// without a slot (slot < 0: the idle entries that pad a captured batch) gets zeros and keeps nothing.
+#include <math.h>
+
+#include "nhv_common.cuh"
+
+constexpr int DS_THREADS = 128;
+constexpr int DS_LANES = 8;
+constexpr int DS_COLS = DS_THREADS / DS_LANES;
+constexpr int DS_TOKENS = 16;
+
+template <typename T, int KPL>
+__global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
+    float* __restrict__ o, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int ld,
+    const float* __restrict__ w_tok, const float* __restrict__ w_head, const T* __restrict__ bonus,
+    float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int H, int dk, int dv, int act_silu, int read_after) {
+  constexpr int DKP = KPL * DS_LANES;                 // key channels with padding (zeros)
+  constexpr int TOK = KPL >= 32 ? DS_TOKENS / 2 : DS_TOKENS;      // the widest heads stage fewer tokens (48 KB of static shared memory)
+  __shared__ __align__(16) float rs[TOK][DKP];
+  __shared__ __align__(16) float ks[TOK][DKP];
+  __shared__ __align__(16) float ws[TOK][DKP];
+  __shared__ float vs[TOK][DS_COLS];
+  __shared__ float cs[TOK];
+  pdl_prologue();
+  const int seq = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * DS_COLS;
+  const int first = cu_q[seq], n = cu_q[seq + 1] - first;
+  if (n <= 0) return;
+  const int tid = threadIdx.x, lane = tid & (DS_LANES - 1), cl = tid / DS_LANES;
+  const int col = col0 + cl;
+  const int slot = slots[seq];
+  const bool col_ok = col < dv;
+  float S[KPL];
+  float* st = slot >= 0 ? state + (size_t)slot * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk : nullptr;
+#pragma unroll
+  for (int i = 0; i < KPL; ++i) {
+    const int c = (i >> 2) * 32 + lane * 4 + (i & 3);
+    S[i] = (st && col_ok && c < dk && q_start[seq] > 0) ? st[c] : 0.f;
+  }
+  const float wh = w_head ? w_head[h] : 1.f;
+  const int warp = tid >> 5, wl = tid & 31;
+  for (int t0 = 0; t0 < n; t0 += TOK) {
+    const int nt = min(TOK, n - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * DKP; i += DS_THREADS) {
+      const int tt = i / DKP, c = i - tt * DKP;
+      float rv = 0.f, kv = 0.f, wv = 0.f;
+      if (c < dk) {
+        const size_t at = (size_t)(first + t0 + tt) * ld + (size_t)h * dk + c;
+        rv = to_f32<T>(r[at]);
+        kv = to_f32<T>(k[at]);
+        if (act_silu) {
+          rv = rv / (1.0f + expf(-rv));
+          kv = kv / (1.0f + expf(-kv));
+        }
+        wv = w_tok ? w_tok[(size_t)(first + t0 + tt) * H * dk + (size_t)h * dk + c] : wh;
+      }
+      rs[tt][c] = rv;
+      ks[tt][c] = kv;
+      ws[tt][c] = wv;
+    }
+    for (int i = tid; i < nt * DS_COLS; i += DS_THREADS) {
+      const int tt = i / DS_COLS, c = i - tt * DS_COLS;
+      float x = 0.f;
+      if (col0 + c < dv) {
+        x = to_f32<T>(v[(size_t)(first + t0 + tt) * ld + (size_t)h * dv + col0 + c]);
+        if (act_silu) x = x / (1.0f + expf(-x));
+      }
+      vs[tt][c] = x;
+    }
+    __syncthreads();
+    // per token: the current token's own weight c_t (a fixed order of summation), then r' in place of r
+    for (int tt = warp; tt < nt; tt += DS_THREADS / 32) {
+      float part = 0.f;
+      for (int c = wl; c < DKP; c += 32) {
+        const float b = (!read_after && bonus && c < dk) ? to_f32<T>(bonus[(size_t)h * dk + c]) : 1.f;
+        part = fmaf(rs[tt][c] * b, ks[tt][c], part);
+      }
+      part = warp_sum(part);
+      if (wl == 0) cs[tt] = part;
+      if (read_after)
+        for (int c = wl; c < DKP; c += 32) rs[tt][c] *= ws[tt][c];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vt = vs[tt][cl];
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < KPL / 4; ++j) {
+        const float4 r4 = *reinterpret_cast<const float4*>(&rs[tt][j * 32 + lane * 4]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][j * 32 + lane * 4]);
+        const float4 w4 = *reinterpret_cast<const float4*>(&ws[tt][j * 32 + lane * 4]);
+        acc = fmaf(r4.x, S[4 * j + 0], acc);
+        acc = fmaf(r4.y, S[4 * j + 1], acc);
+        acc = fmaf(r4.z, S[4 * j + 2], acc);
+        acc = fmaf(r4.w, S[4 * j + 3], acc);
+        S[4 * j + 0] = fmaf(w4.x, S[4 * j + 0], k4.x * vt);
+        S[4 * j + 1] = fmaf(w4.y, S[4 * j + 1], k4.y * vt);
+        S[4 * j + 2] = fmaf(w4.z, S[4 * j + 2], k4.z * vt);
+        S[4 * j + 3] = fmaf(w4.w, S[4 * j + 3], k4.w * vt);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (lane == 0 && col_ok) o[(size_t)(first + t0 + tt) * H * dv + (size_t)h * dv + col] = fmaf(cs[tt], vt, acc);
+    }
+  }
+  if (st && col_ok) {
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+      const int c = (i >> 2) * 32 + lane * 4 + (i & 3);
+      if (c < dk) st[c] = S[i];
+    }
+  }
+}
+
+NHV_API int nhv_decay_scan(int dtype, float* o, const void* r, const void* k, const void* v, int ld, const float* w_tok,
+                           const float* w_head, const void* bonus, float* state, long state_stride, const int* cu_q,
+                           const int* q_start, const int* slots, int n_seqs, int n_tokens, int H, int dk, int dv,
+                           int act_silu, int read_after, cudaStream_t stream) {
+  if (n_tokens == 0 || n_seqs == 0) return 0;
+  NHV_REQUIRE(H > 0 && dk > 0 && dv > 0 && dk <= 256, "decay_scan: key heads of 1 to 256 channels, got %d", dk);
+  NHV_REQUIRE((w_tok != nullptr) != (w_head != nullptr), "decay_scan: the decay is a tensor per token or a constant per head");
+  NHV_REQUIRE(state && state_stride >= (long)H * dk * dv, "decay_scan: the state holds H dk dv floats per request");
+  dim3 grid((dv + DS_COLS - 1) / DS_COLS, H, n_seqs);
+#define LAUNCH(T, KPL)                                                                                               \
+  nhv_launch(decay_scan_kernel<T, KPL>, grid, DS_THREADS, 0, stream, o, (const T*)r, (const T*)k, (const T*)v, ld,   \
+             w_tok, w_head, (const T*)bonus, state, state_stride, cu_q, q_start, slots, H, dk, dv, act_silu, read_after)
+#define LAUNCH_K(T)                    \
+  do {                                 \
+    if (dk <= 32) LAUNCH(T, 4);        \
+    else if (dk <= 64) LAUNCH(T, 8);   \
+    else if (dk <= 128) LAUNCH(T, 16); \
+    else LAUNCH(T, 32);                \
+  } while (0)
+  if (dtype == NHV_F32) LAUNCH_K(float);
+  else if (dtype == NHV_BF16) LAUNCH_K(__nv_bfloat16);
+  else NHV_REQUIRE(false, "decay_scan: unknown dtype %d", dtype);
+#undef LAUNCH_K
+#undef LAUNCH
+  NHV_CHECK_LAUNCH("decay_scan");
+  return 0;
+}
+
+template <typename T>
+__global__ void decay_lowrank_kernel(float* __restrict__ w, const float* __restrict__ inner, int inner_stride,
+                                     const T* __restrict__ w2, const T* __restrict__ w0, int n_tokens, int n, int rank) {
+  extern __shared__ float th[];                       // tanh of the token's inner projection
+  pdl_prologue();
+  const int t = blockIdx.x;
+  for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(inner[(size_t)t * inner_stride + j]);
+  __syncthreads();
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
+    float z = to_f32<T>(w0[c]);
+    const T* row = w2 + (size_t)c * rank;
+    for (int j = 0; j < rank; ++j) z = fmaf(th[j], to_f32<T>(row[j]), z);
+    w[(size_t)t * n + c] = expf(-expf(z));
+  }
+}
+
+NHV_API int nhv_decay_lowrank(int dtype, float* w, const float* inner, int inner_stride, const void* w2, const void* w0,
+                              int n_tokens, int n, int rank, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  NHV_REQUIRE(n > 0 && rank > 0 && rank <= 8192 && inner_stride >= rank, "decay_lowrank: bad sizes (n %d, rank %d)", n, rank);
+  const int threads = 128;
+  dim3 grid(n_tokens, (n + threads - 1) / threads > 8 ? 8 : (n + threads - 1) / threads);
+  const size_t smem = (size_t)rank * sizeof(float);
+  if (dtype == NHV_F32)
+    nhv_launch(decay_lowrank_kernel<float>, grid, threads, smem, stream, w, inner, inner_stride, (const float*)w2,
+               (const float*)w0, n_tokens, n, rank);
+  else if (dtype == NHV_BF16)
+    nhv_launch(decay_lowrank_kernel<__nv_bfloat16>, grid, threads, smem, stream, w, inner, inner_stride,
+               (const __nv_bfloat16*)w2, (const __nv_bfloat16*)w0, n_tokens, n, rank);
+  else NHV_REQUIRE(false, "decay_lowrank: unknown dtype %d", dtype);
+  NHV_CHECK_LAUNCH("decay_lowrank");
+  return 0;
+}

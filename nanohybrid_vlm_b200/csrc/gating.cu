@@ -201,6 +201,40 @@ NHV_API int nhv_relu_squared(int dtype, void* x, size_t total, cudaStream_t stre
   return 0;
 }
 
+// x = gelu_tanh(x) in place, gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), computed in fp32 and rounded
+// once (the unit of a feed-forward without a gate).
+__device__ __forceinline__ float gating_gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T, int VEC>
+__global__ void gelu_tanh_kernel(T* __restrict__ x, size_t total) {
+  pdl_prologue();
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < total; i += (size_t)gridDim.x * blockDim.x * VEC) {
+    if constexpr (VEC == 8) {
+      float v[8];
+      nhv_load8(v, x + i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = gating_gelu_tanh(v[e]);
+      nhv_store8(x + i, v);
+    } else {
+      x[i] = from_f32<T>(gating_gelu_tanh(to_f32<T>(x[i])));
+    }
+  }
+}
+
+NHV_API int nhv_gelu_tanh(int dtype, void* x, size_t total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const bool vec = total % 8 == 0 && aligned16(x);
+#define GO(T, V) nhv_launch(gelu_tanh_kernel<T, V>, gating_blocks(total / V), 256, 0, stream, (T*)x, total)
+  if (dtype == NHV_F32) { if (vec) GO(float, 8); else GO(float, 1); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
+  else NHV_REQUIRE(false, "gelu_tanh: unknown dtype %d", dtype);
+#undef GO
+  NHV_CHECK_LAUNCH("gelu_tanh");
+  return 0;
+}
+
 // Logits in place (fp32): z <- z * scale, then, with cap > 0, z <- cap * tanh(z / cap).
 __global__ void scale_softcap_kernel(float* __restrict__ z, float scale, float cap, size_t total) {
   pdl_prologue();

@@ -6,12 +6,17 @@
 //                 neighbours, a group's score is its largest c, and only outputs of the `keep` best groups can be
 //                 chosen (the others count as -inf); the `top` outputs with the largest c are chosen; their weights
 //                 are their s, divided by the sum of the chosen s (+ 1e-20).  One warp per token, all in fp32.
+//                 sigmoid_scores: s = sigmoid(z) instead of the softmax; renorm 0: the weights are the chosen s as
+//                 they are.
 //   moe_align     slots (t, k) whose choice is a real expert are grouped by expert; each expert's run is padded to
 //                 a multiple of the row tile, so that a tile of rows has one expert.  Writes sorted_slots (slot per
 //                 row, -1 for padding), slot_pos (row per slot, -1 for identity choices) and tile_expert.
 //   moe_gemm      (any type, CUDA cores, fixed order of summation over k) the products over the sorted rows:
 //                 first: act[row] = glu(x[token(row)] Wg[e]^T, x[token(row)] Wu[e]^T), second: y[row] = act[row] Wd[e]^T.
-//   moe_combine   out[t] = sum_k w[t,k] * (choice is an expert ? y[row(t,k)] : x[t]) + sigmoid(sg[t]) * shared[t].
+//                 row_scale [slots] (optional): a factor on the expert's input, one per (token, choice) slot; it is
+//                 applied to both first products' fp32 sums, which equals scaling the input.
+//   moe_combine   out[t] = sum_k w[t,k] * (choice is an expert ? y[row(t,k)] : x[t]) + sigmoid(sg[t]) * shared[t];
+//                 without weights every choice counts fully (the weights went into the experts' inputs).
 //
 // A row's result does not depend on where in its expert's run it stands, so the order in which moe_align hands out
 // rows (atomics) does not show in the numbers.
@@ -34,7 +39,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 
 __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
     int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits, int ld,
-    const float* __restrict__ correction, int n_tokens, int N, int n_groups, int keep, int top) {
+    const float* __restrict__ correction, int n_tokens, int N, int n_groups, int keep, int top, int sigmoid_scores,
+    int renorm) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -44,20 +50,28 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
   float* c = s + N;                          // choice scores
   float* gs = c + N;                         // group scores
   const float* z = logits + (size_t)t * ld;
-  float mx = -INFINITY;
-  for (int j = lane; j < N; j += 32) mx = fmaxf(mx, z[j]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int j = lane; j < N; j += 32) {
-    const float e = expf(z[j] - mx);
-    s[j] = e;
-    sum += e;
-  }
-  sum = warp_sum(sum);
-  for (int j = lane; j < N; j += 32) {
-    const float v = s[j] / sum;
-    s[j] = v;
-    c[j] = v + (correction ? correction[j] : 0.f);
+  if (sigmoid_scores) {
+    for (int j = lane; j < N; j += 32) {
+      const float v = 1.0f / (1.0f + expf(-z[j]));
+      s[j] = v;
+      c[j] = v + (correction ? correction[j] : 0.f);
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int j = lane; j < N; j += 32) mx = fmaxf(mx, z[j]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int j = lane; j < N; j += 32) {
+      const float e = expf(z[j] - mx);
+      s[j] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    for (int j = lane; j < N; j += 32) {
+      const float v = s[j] / sum;
+      s[j] = v;
+      c[j] = v + (correction ? correction[j] : 0.f);
+    }
   }
   __syncwarp();
   if (n_groups > 1 && keep < n_groups) {
@@ -102,12 +116,13 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
     }
     __syncwarp();
   }
+  if (!renorm) return;
   const float inv = 1.0f / (wsum + 1e-20f);
   for (int r = lane; r < top; r += 32) weights[(size_t)t * top + r] *= inv;
 }
 
 NHV_API int nhv_moe_route(int* ids, float* weights, const float* logits, int ld, const float* correction, int n_tokens, int N,
-                          int n_groups, int keep, int top, cudaStream_t stream) {
+                          int n_groups, int keep, int top, int sigmoid_scores, int renorm, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(N > 0 && N <= 4096 && top > 0 && top <= N && ld >= N, "moe_route: bad sizes (N %d, top %d)", N, top);
   NHV_REQUIRE(n_groups > 0 && N % n_groups == 0 && keep > 0 && keep <= n_groups,
@@ -117,7 +132,7 @@ NHV_API int nhv_moe_route(int* ids, float* weights, const float* logits, int ld,
   if (smem > 48 * 1024)
     NHV_CUDA(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "moe_route");
   nhv_launch(moe_route_kernel, (n_tokens + MR_WARPS - 1) / MR_WARPS, MR_WARPS * 32, smem, stream, ids, weights, logits, ld,
-             correction, n_tokens, N, n_groups, keep, top);
+             correction, n_tokens, N, n_groups, keep, top, sigmoid_scores, renorm);
   NHV_CHECK_LAUNCH("moe_route");
   return 0;
 }
@@ -190,11 +205,8 @@ constexpr int MG_BM = 16;
 constexpr int MG_BN = 64;
 constexpr int MG_BK = 32;
 
-__device__ __forceinline__ float moe_glu(float g, float u, float limit, float alpha) {
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-}
+#include "nhv_glu.cuh"
+
 
 // FIRST: A rows are x[sorted_slots[row] / top], B = (Wg[e], Wu[e]) [N, K] each, out = glu.  Else: A rows are
 // a[row], B = Wd[e] [N, K].  256 threads: thread (ty, tx) has rows ty * 4 .. + 3 of column tx.
@@ -202,8 +214,9 @@ template <typename T, bool FIRST>
 __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(
     T* __restrict__ out, const T* __restrict__ A, int lda, const T* __restrict__ W0, const T* __restrict__ W1,
     const int* __restrict__ sorted_slots, const int* __restrict__ tile_expert, int top, int N, int K, float limit,
-    float alpha) {
+    float alpha, float up_shift, const float* __restrict__ row_scale) {
   __shared__ float As[MG_BM][MG_BK + 1];
+  __shared__ float ascale[MG_BM];
   __shared__ float B0[MG_BN][MG_BK + 1];
   __shared__ float B1[FIRST ? MG_BN : 1][MG_BK + 1];
   __shared__ int arow[MG_BM];
@@ -216,6 +229,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(
     const int row = tile * MG_BM + tid;
     const int slot = sorted_slots[row];
     arow[tid] = slot < 0 ? -1 : (FIRST ? slot / top : row);
+    ascale[tid] = (FIRST && row_scale && slot >= 0) ? row_scale[slot] : 1.f;
   }
   __syncthreads();
   const T* w0 = W0 + (size_t)e * N * K;
@@ -254,7 +268,8 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(
     if (arow[lr] < 0) continue;
     const size_t row = (size_t)tile * MG_BM + lr;
     // the storage type's rounding of gate and up comes first, as a separate product would leave it
-    const float v = FIRST ? moe_glu(round_to<T>(acc0[r]), round_to<T>(acc1[r]), limit, alpha) : acc0[r];
+    const float sc = ascale[lr];          // a factor on the expert's input is a factor on both first products
+    const float v = FIRST ? nhv_glu(round_to<T>(sc * acc0[r]), round_to<T>(sc * acc1[r]), limit, alpha, up_shift) : acc0[r];
     out[row * N + n0 + tx] = from_f32<T>(v);
   }
 }
@@ -265,14 +280,14 @@ NHV_API int nhv_moe_simt_tile() { return MG_BM; }
 // = a [rows, K] times W0 [E, N, K].  max_tiles: the tiles of the ordering (rows / tile).
 NHV_API int nhv_moe_gemm_simt(int dtype, int first, void* out, const void* A, int lda, const void* W0, const void* W1,
                               const int* sorted_slots, const int* tile_expert, int max_tiles, int top, int N, int K,
-                              float limit, float alpha, cudaStream_t stream) {
+                              float limit, float alpha, float up_shift, const float* row_scale, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   NHV_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && top > 0, "moe_gemm: bad sizes");
   dim3 grid(max_tiles, (N + MG_BN - 1) / MG_BN);
   NHV_REQUIRE(grid.y <= 65535, "moe_gemm: %d output columns are beyond the grid's reach", N);
 #define GO(T, F)                                                                                                 \
   nhv_launch(moe_gemm_simt_kernel<T, F>, grid, 256, 0, stream, (T*)out, (const T*)A, lda, (const T*)W0, (const T*)W1, \
-             sorted_slots, tile_expert, top, N, K, limit, alpha)
+             sorted_slots, tile_expert, top, N, K, limit, alpha, up_shift, row_scale)
   if (dtype == NHV_F32) { if (first) GO(float, true); else GO(float, false); }
   else if (dtype == NHV_BF16) { if (first) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false); }
   else NHV_REQUIRE(false, "moe_gemm: unknown dtype %d", dtype);
@@ -295,7 +310,7 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
   float* w = smem;                            // [top]
   int* pos = reinterpret_cast<int*>(smem + top);
   for (int k = threadIdx.x; k < top; k += blockDim.x) {
-    w[k] = weights[(size_t)t * top + k];
+    w[k] = weights ? weights[(size_t)t * top + k] : 1.f;
     const int e = ids[(size_t)t * top + k];
     pos[k] = e < E ? slot_pos[(size_t)t * top + k] : -2;      // -2: an identity expert
   }

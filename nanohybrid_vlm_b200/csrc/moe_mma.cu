@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "nhv_common.cuh"
+#include "nhv_glu.cuh"
 
 typedef __nv_bfloat16 bf16;
 
@@ -42,11 +43,6 @@ __device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], ui
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ float mm_glu(float g, float u, float limit, float alpha) {
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-}
 __device__ __forceinline__ float mm_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 template <int BM> struct MmShape {
@@ -58,12 +54,13 @@ template <int BM, bool FIRST>
 __global__ void __launch_bounds__(MmShape<BM>::THREADS) moe_gemm_mma_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ A, int lda, const bf16* __restrict__ W0, const bf16* __restrict__ W1,
     const int* __restrict__ sorted_slots, const int* __restrict__ tile_expert, int top, int N, int K, float limit,
-    float alpha) {
+    float alpha, float up_shift, const float* __restrict__ row_scale) {
   constexpr int MT = MmShape<BM>::WM / 16, MM_THREADS = MmShape<BM>::THREADS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* As = reinterpret_cast<bf16*>(smem_raw);              // [STAGES][BM][LDS]
   bf16* Bs = As + MM_STAGES * BM * MM_LDS;                   // [STAGES][BROWS][LDS]
   __shared__ int arow[BM];
+  __shared__ float ascale[BM];                              // a factor on the expert's input, per row (1 without)
   pdl_prologue();
   // panels of one tile of rows are neighbours in the grid: they run together and share the tile's rows in L2
   const int tile = blockIdx.y;
@@ -76,6 +73,7 @@ __global__ void __launch_bounds__(MmShape<BM>::THREADS) moe_gemm_mma_kernel(
     const int row = tile * BM + tid;
     const int slot = sorted_slots[row];
     arow[tid] = slot < 0 ? -1 : (FIRST ? slot / top : row);
+    ascale[tid] = (FIRST && row_scale && slot >= 0) ? row_scale[slot] : 1.f;
   }
   __syncthreads();
   const bf16* w0 = W0 + (size_t)e * N * K;
@@ -151,6 +149,7 @@ __global__ void __launch_bounds__(MmShape<BM>::THREADS) moe_gemm_mma_kernel(
     for (int half = 0; half < 2; ++half) {
       const int lr = row0 + mt * 16 + g + 8 * half;
       if (arow[lr] < 0) continue;
+      const float sc = ascale[lr];
       bf16* orow = out + ((size_t)tile * BM + lr) * N;
 #pragma unroll
       for (int j = 0; j < (FIRST ? 2 : 4); ++j) {
@@ -159,8 +158,8 @@ __global__ void __launch_bounds__(MmShape<BM>::THREADS) moe_gemm_mma_kernel(
         float v0, v1;
         if (FIRST) {
           // gate and up rounded to the storage type first, as a separate product would leave them
-          v0 = mm_glu(mm_round(acc[mt][j][2 * half]), mm_round(acc[mt][j + 2][2 * half]), limit, alpha);
-          v1 = mm_glu(mm_round(acc[mt][j][2 * half + 1]), mm_round(acc[mt][j + 2][2 * half + 1]), limit, alpha);
+          v0 = nhv_glu(mm_round(sc * acc[mt][j][2 * half]), mm_round(sc * acc[mt][j + 2][2 * half]), limit, alpha, up_shift);
+          v1 = nhv_glu(mm_round(sc * acc[mt][j][2 * half + 1]), mm_round(sc * acc[mt][j + 2][2 * half + 1]), limit, alpha, up_shift);
         } else {
           v0 = acc[mt][j][2 * half];
           v1 = acc[mt][j][2 * half + 1];
@@ -179,7 +178,7 @@ static size_t mm_smem_bytes() { return (size_t)MM_STAGES * (BM + MM_BROWS) * MM_
 // by sorted_slots, W0 / W1 [E, N, K]; first == 0: out [rows, N] = a [rows, K] times W0 [E, N, K].
 NHV_API int nhv_moe_gemm_mma(int tile, int first, void* out, const void* A, int lda, const void* W0, const void* W1,
                              const int* sorted_slots, const int* tile_expert, int max_tiles, int top, int N, int K,
-                             float limit, float alpha, cudaStream_t stream) {
+                             float limit, float alpha, float up_shift, const float* row_scale, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   NHV_REQUIRE(tile == 16 || tile == 64 || tile == 128, "moe_gemm (mma): the row tile is 16, 64 or 128, not %d", tile);
   NHV_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && top > 0, "moe_gemm (mma): bad sizes");
@@ -197,7 +196,8 @@ NHV_API int nhv_moe_gemm_mma(int tile, int first, void* out, const void* A, int 
       attr = true;                                                                                                    \
     }                                                                                                                 \
     nhv_launch(moe_gemm_mma_kernel<BM, F>, grid, MmShape<BM>::THREADS, mm_smem_bytes<BM>(), stream, (bf16*)out, (const bf16*)A, \
-               lda, (const bf16*)W0, (const bf16*)W1, sorted_slots, tile_expert, top, N, K, limit, alpha);            \
+               lda, (const bf16*)W0, (const bf16*)W1, sorted_slots, tile_expert, top, N, K, limit, alpha, up_shift,   \
+               row_scale);                                                                                            \
   } while (0)
   if (tile == 16) { if (first) GO(16, true); else GO(16, false); }
   else if (tile == 64) { if (first) GO(64, true); else GO(64, false); }

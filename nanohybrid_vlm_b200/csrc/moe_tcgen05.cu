@@ -21,6 +21,7 @@
 
 #define NHV_WAIT_LIMIT (1u << 22)
 #include "nhv_async.cuh"
+#include "nhv_glu.cuh"
 
 namespace {
 
@@ -89,11 +90,6 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n) {
 }
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(EPI_THREADS) : "memory"); }
 
-__device__ __forceinline__ float glu(float g, float u, float limit, float alpha) {
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-}
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 struct alignas(64) Params {
@@ -104,7 +100,8 @@ struct alignas(64) Params {
   const int* sorted_slots;
   const int* tile_expert;
   int N, K;
-  float limit, alpha;
+  float limit, alpha, up_shift;
+  const float* row_scale;     // a factor on the expert's input per (token, choice) slot, or null
 };
 
 template <bool FIRST>
@@ -118,6 +115,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tcgen05_kernel(const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   __shared__ int s_abort;
   __shared__ int s_epi_abort;             // set by epilogue threads only, read by them after their barrier: one answer for all
+  __shared__ float s_scale[ROWS];         // the row's factor on the expert's input (1 without)
   __shared__ int s_live[ROWS];            // 1 where the row of the tile is a slot, 0 where it is padding
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -193,7 +191,11 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tcgen05_kernel(const __grid_co
       const int tid = threadIdx.x - 64;                         // 0..127
       const int quarter = warp & 3;                             // the tensor-memory lanes this warp may read
       const int lane_row = quarter * 32 + lane;                 // the weight row of the panel that this thread holds
-      s_live[tid] = p.sorted_slots[(size_t)tile * ROWS + tid] >= 0;
+      {
+        const int slot = p.sorted_slots[(size_t)tile * ROWS + tid];
+        s_live[tid] = slot >= 0;
+        s_scale[tid] = (FIRST && p.row_scale && slot >= 0) ? p.row_scale[slot] : 1.f;
+      }
       if (!mbar_wait(acc_full, 0, 4)) s_epi_abort = 1;
       epi_sync();
       const bool ok = s_epi_abort == 0;                         // the same for all 128: they meet at barriers below
@@ -217,7 +219,9 @@ __global__ void __launch_bounds__(THREADS, 1) moe_tcgen05_kernel(const __grid_co
               for (int j = 0; j < 32; ++j)
                 if (s_live[c0 + j]) {
                   // gate and up rounded to the storage type first, as a separate product would leave them
-                  const float a = glu(round_bf16(v[j]), round_bf16(park[lane_row * PARK_LD + j]), p.limit, p.alpha);
+                  const float sc = s_scale[c0 + j];
+                  const float a = nhv_glu(round_bf16(sc * v[j]), round_bf16(sc * park[lane_row * PARK_LD + j]), p.limit, p.alpha,
+                                          p.up_shift);
                   p.out[((size_t)tile * ROWS + c0 + j) * p.N + n] = __float2bfloat16_rn(a);
                 }
             }
@@ -306,7 +310,7 @@ NHV_API int nhv_moe_gather_rows(void* out, const void* x, const int* sorted_slot
 // first == 0: out [rows, N] = A W0[e]^T.  rows = tiles * 128, the ordering of moe_align with tiles of 128 rows.
 NHV_API int nhv_moe_gemm_tcgen05(int first, void* out, const void* A, const void* W0, const void* W1, int n_experts,
                                  const int* sorted_slots, const int* tile_expert, int tiles, int N, int K, float limit,
-                                 float alpha, cudaStream_t stream) {
+                                 float alpha, float up_shift, const float* row_scale, cudaStream_t stream) {
   if (tiles == 0) return 0;
   NHV_REQUIRE(tiles > 0 && N > 0 && K > 0 && K % 8 == 0 && n_experts > 0, "moe_gemm (tcgen05): K must be a multiple of 8 (N=%d K=%d)", N, K);
   NHV_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W0 % 16) == 0 && (!first || ((uintptr_t)W1 % 16) == 0),
@@ -325,6 +329,8 @@ NHV_API int nhv_moe_gemm_tcgen05(int first, void* out, const void* A, const void
   p.K = K;
   p.limit = limit;
   p.alpha = alpha;
+  p.up_shift = up_shift;
+  p.row_scale = row_scale;
   dim3 grid((N + box - 1) / box, tiles);
   NHV_REQUIRE(grid.y <= 65535, "moe_gemm (tcgen05): %d tiles of rows are beyond the grid's reach", tiles);
   static bool attr_set = false;

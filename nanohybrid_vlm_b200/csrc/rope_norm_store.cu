@@ -7,6 +7,8 @@
 //   k heads: the same -> the token's slot of the K pages
 //   v heads: copied -> the token's slot of the V pages
 // eps < 0 leaves the norm out.  Rotation and norm are computed in fp32 and rounded once.
+// norm_first: the norm (with its weight) comes before the rotation instead of after it.  interleaved: element 2i turns
+// with element 2i + 1 (the table is the same: cos then sin of angle i).
 // q_weight / k_weight (optional, [dk], shared by the heads of their kind): the normed head times this weight.
 // bias (optional, [nq*dk + nkv*dk], the query and key columns of qkv): added in fp32 to what the projection gave,
 // before anything else (projected values have none).  v_from_k: the values are the key heads as projected (with their bias, before the rotation); qkv
@@ -26,7 +28,7 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
                                        int n_tokens, int nq, int nkv, int dk, int dv, int row, int page_size,
                                        int n_pages, float eps, int heads_per_token, const T* __restrict__ bias,
                                        int v_from_k, const T* __restrict__ q_weight,
-                                       const T* __restrict__ k_weight) {
+                                       const T* __restrict__ k_weight, int norm_first, int interleaved) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -61,6 +63,16 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
   float ss = 0.f;
   float mine[RN_MAX_D / 32];
   if (kind != 2) {
+    const T* hw = kind == 0 ? q_weight : k_weight;
+    if (norm_first && eps >= 0.f) {
+      // the norm (and its weight) before the rotation: the head in shared memory is replaced by its normed self
+      float s0 = 0.f;
+      for (int c = lane; c < d; c += 32) s0 = fmaf(v[c], v[c], s0);
+      s0 = warp_sum(s0);
+      const float r0 = 1.0f / sqrtf(s0 / (float)d + eps);
+      for (int c = lane; c < d; c += 32) v[c] = hw ? v[c] * r0 * to_f32<T>(hw[c]) : v[c] * r0;
+      __syncwarp();
+    }
     const float* cs = nullptr;
     const int half = rotary_dim >> 1;
     if (cos_sin) {
@@ -74,15 +86,18 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
       float yv = 0.f;
       if (c < d) {
         yv = v[c];
-        if (cs && c < half) yv = v[c] * cs[c] - v[c + half] * cs[half + c];
+        if (cs && interleaved && c < rotary_dim) {
+          const int i = c >> 1;                                 // the pair (2i, 2i + 1) turns by angle i
+          yv = (c & 1) ? v[c] * cs[i] + v[c - 1] * cs[half + i] : v[c] * cs[i] - v[c + 1] * cs[half + i];
+        } else if (cs && c < half) yv = v[c] * cs[c] - v[c + half] * cs[half + c];
         else if (cs && c < rotary_dim) yv = v[c] * cs[c - half] + v[c - half] * cs[c];
         ss = fmaf(yv, yv, ss);
       }
       mine[k] = yv;
     }
     ss = warp_sum(ss);
-    const float r = eps >= 0.f ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
-    const T* hw = kind == 0 ? q_weight : k_weight;
+    const float r = eps >= 0.f && !norm_first ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    if (norm_first) hw = nullptr;
 #pragma unroll
     for (int k = 0; k < RN_MAX_D / 32; ++k) {
       const int c = lane + k * 32;
@@ -98,7 +113,8 @@ NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void
                                 void* kv_pages, const int* slot_mapping, const int* positions, const float* cos_sin,
                                 int rotary_dim, int max_position, int n_tokens, int nq, int nkv, int dk, int dv, int row,
                                 int page_size, int n_pages, float eps, const void* bias, int v_from_k,
-                                const void* q_weight, const void* k_weight, cudaStream_t stream) {
+                                const void* q_weight, const void* k_weight, int norm_first, int interleaved,
+                                cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(n_tokens > 0 && nq > 0 && nkv >= 0 && dk > 0 && dv > 0, "rope_norm_store: bad sizes");
   NHV_REQUIRE(dk <= RN_MAX_D && dv <= RN_MAX_D, "rope_norm_store: head sizes %d / %d are beyond the supported %d", dk, dv, RN_MAX_D);
@@ -116,7 +132,7 @@ NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void
   nhv_launch(rope_norm_store_kernel<T>, blocks, RN_WARPS * 32, smem, stream, (const T*)qkv, qkv_stride, (T*)q_out, \
              q_out_stride, (T*)kv_pages, slot_mapping, positions, cos_sin, rotary_dim, max_position, n_tokens, nq, \
              nkv, dk, dv, row, page_size, n_pages, eps, heads_per_token, (const T*)bias, v_from_k, (const T*)q_weight,    \
-             (const T*)k_weight)
+             (const T*)k_weight, norm_first, interleaved)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
   else NHV_REQUIRE(false, "rope_norm_store: unknown dtype %d", dtype);

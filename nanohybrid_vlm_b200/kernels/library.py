@@ -42,7 +42,7 @@ _SIGNATURES = {
     "nhv_delta_rule": [I, P, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P],
     "nhv_ssd_scan": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, I, I, P],
     "nhv_gated_rmsnorm": [I, P, I, P, P, I, P, I, I, I, I, F, I, I, P],
-    "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, I, P, P, P],
+    "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, I, P, P, I, I, P],
     "nhv_dyntanh": [I, I, I, P, P, P, P, P, I, I, P],
     "nhv_embed_dyntanh": [I, P, P, P, P, P, P, I, I, I, P],
     "nhv_dyntanh_stream": [I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
@@ -50,14 +50,14 @@ _SIGNATURES = {
     "nhv_add_row_bias": [I, P, P, I, I, P],
     "nhv_clamped_glu": [I, P, P, I, I, F, F, P],
     "nhv_mlstm_scan": [I, P, P, I, P, I, P, F, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, P],
-    "nhv_moe_route": [P, P, P, I, P, I, I, I, I, I, P],
+    "nhv_moe_route": [P, P, P, I, P, I, I, I, I, I, I, I, P],
     "nhv_moe_align": [P, I, I, I, P, P, P, P],
-    "nhv_moe_gemm_simt": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
-    "nhv_moe_gemm_mma": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
+    "nhv_moe_gemm_simt": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, F, P, P],
+    "nhv_moe_gemm_mma": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, F, P, P],
     "nhv_moe_gather_rows": [P, P, P, I, I, I, P],
-    "nhv_moe_gemm_tcgen05": [I, P, P, P, P, I, P, P, I, I, I, F, F, P],
+    "nhv_moe_gemm_tcgen05": [I, P, P, P, P, I, P, P, I, I, I, F, F, F, P, P],
     "nhv_moe_combine": [I, P, P, P, P, P, I, P, P, P, I, I, I, I, P],
-    "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P],
+    "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I, I, P],
     "nhv_causal_filter_add": [I, P, P, I, P, I, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
     "nhv_latent_rope_store": [I, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "nhv_gemm_nt_simt_batched": [I, P, P, P, I, I, I, I, I, I, I, I, ctypes.c_long, ctypes.c_long, ctypes.c_long, P],
@@ -70,6 +70,12 @@ _SIGNATURES = {
     "nhv_latent_decode": [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, P, I, P, P, P],
     "nhv_relu_squared": [I, P, c_size_t, P],
     "nhv_scale_softcap": [P, F, F, c_size_t, P],
+    "nhv_gelu_tanh": [I, P, c_size_t, P],
+    "nhv_postnorm_stream": [I, P, P, P, P, F, P, P, F, P, P, I, I, F, F, P],
+    "nhv_stream_round": [I, P, P, c_size_t, P],
+    "nhv_token_shift_mix": [I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
+    "nhv_decay_scan": [I, P, P, P, P, I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, I, P],
+    "nhv_decay_lowrank": [I, P, P, I, P, P, I, I, I, P],
 }
 
 

@@ -428,6 +428,98 @@ def latent_attention(out, q_lat, pages, tables, batch, H: int, rank: int, row: i
          part.data_ptr(), part.data_ptr() + 4 * T * H * pieces * rank, stream_ptr())
 
 
+def gelu_tanh(x) -> None:
+    """x = 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))) in place."""
+    _need_cuda(x)
+    _contig("x", x)
+    call("nhv_gelu_tanh", dtype_code(x), x.data_ptr(), x.numel(), stream_ptr())
+
+
+def postnorm_stream(stream, rounded, terms, weight, scale, eps: float, side_eps: float | None = None) -> None:
+    """A sub-block's output normed and added onto a float32 residual stream [T, width], in place:
+    y = sum over ``terms`` ((tensor, coef, side weight or None), one or two) of coef * tensor, a term with a side weight
+    first divided by its own root mean square and multiplied by that weight; stream += y / rms(y) * weight (* scale, a
+    vector per channel, if given).  ``rounded`` (optional, storage type): receives the new stream rounded once, what the
+    next sub-block reads.  All sums and norms are 32-bit."""
+    tensors = [t for t, _, _ in terms] + [w for _, _, w in terms]
+    _need_cuda(stream, rounded, weight, scale, *tensors)
+    _contig("stream", stream)
+    width = stream.shape[-1]
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("the output norm adds one or two terms")
+    (a, ca, wa), (b, cb, wb) = terms[0], (terms[1] if len(terms) == 2 else (None, 0.0, None))
+    assert stream.dtype == torch.float32 and weight.numel() == width and weight.dtype == a.dtype
+    for t in (a, b):
+        assert t is None or (t.shape == stream.shape and t.is_contiguous() and t.dtype == a.dtype)
+    for w in (wa, wb, scale):
+        assert w is None or (w.numel() == width and w.dtype == a.dtype and w.is_contiguous())
+    assert rounded is None or (rounded.shape == stream.shape and rounded.dtype == a.dtype and rounded.is_contiguous())
+    if wa is None and wb is not None:
+        raise KernelError("a side norm on the second term only is not offered")
+    call("nhv_postnorm_stream", dtype_code(a), stream.data_ptr(), _ptr(rounded), a.data_ptr(), _ptr(wa), float(ca), _ptr(b),
+         _ptr(wb), float(cb), weight.data_ptr(), _ptr(scale), stream.numel() // width, width, float(eps),
+         float(eps if side_eps is None else side_eps), stream_ptr())
+
+
+def stream_round(out, stream) -> None:
+    """out (storage type) = the float32 stream rounded once."""
+    _need_cuda(out, stream)
+    _contig("out", out); _contig("stream", stream)
+    assert stream.dtype == torch.float32 and out.numel() == stream.numel()
+    call("nhv_stream_round", dtype_code(out), out.data_ptr(), stream.data_ptr(), stream.numel(), stream_ptr())
+
+
+def token_shift_mix(out, x, mu, state, batch) -> None:
+    """out [T, n, C]: out[t, s] = x[t] + (x[t - 1] - x[t]) * mu[s] for mu [n, C]; the token before a request's first
+    is zero, the one before this step's portion is the request's ``state`` [slots, C] float32, which is moved on."""
+    _need_cuda(out, x, mu, state)
+    _contig("out", out); _contig("x", x); _contig("mu", mu)
+    T, C = x.shape
+    n = mu.shape[0]
+    assert out.shape == (T, n, C) and mu.shape == (n, C) and out.dtype == x.dtype == mu.dtype
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= C
+    call("nhv_token_shift_mix", dtype_code(x), out.data_ptr(), x.data_ptr(), mu.data_ptr(), state.data_ptr(), state.stride(0),
+         batch.cu_q.data_ptr(), batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, C, n, stream_ptr())
+
+
+def decay_lowrank(w, inner, w2, w0) -> None:
+    """w [T, n] float32 = exp(-exp(w0 + tanh(inner) @ w2^T)) for inner [T, rank] float32 (a view with unit column
+    stride), w2 [n, rank] and w0 [n] in the storage type: a decay per token and channel from the sums of its inner
+    projection, tanh and both exponentials in 32-bit."""
+    _need_cuda(w, inner, w2, w0)
+    _contig("w", w); _contig("w2", w2); _contig("w0", w0)
+    T, rank = inner.shape
+    n = w2.shape[0]
+    assert w.dtype == inner.dtype == torch.float32 and inner.stride(1) == 1 and w.shape == (T, n)
+    assert w2.shape == (n, rank) and w0.numel() == n and w2.dtype == w0.dtype
+    call("nhv_decay_lowrank", dtype_code(w2), w.data_ptr(), inner.data_ptr(), inner.stride(0), w2.data_ptr(), w0.data_ptr(),
+         T, n, rank, stream_ptr())
+
+
+def decay_scan(o, r, k, v, state, batch, H: int, dk: int, dv: int, decay_tokens=None, decay_heads=None, bonus=None,
+               silu: bool = False, read_after: bool = False) -> None:
+    """A linear recurrence with a matrix state per head over the step's tokens: S <- diag(w) S + k v^T, with
+    o = (S_before + diag(bonus) k v^T)^T r (``read_after`` False; no bonus: ones) or o = S_after^T r (True).
+    r, k [T, H dk] and v [T, H dv]: views into one projection output (same row stride, unit column stride, storage type),
+    through SiLU if ``silu``.  The decay w: ``decay_tokens`` [T, H dk] float32 or ``decay_heads`` [H] float32.
+    state [slots, H dv dk] float32 -> o [T, H dv] float32."""
+    _need_cuda(o, r, k, v, state, decay_tokens, decay_heads, bonus)
+    T = r.shape[0]
+    assert r.shape == k.shape == (T, H * dk) and v.shape == (T, H * dv) and r.dtype == k.dtype == v.dtype
+    assert r.stride(1) == k.stride(1) == v.stride(1) == 1 and r.stride(0) == k.stride(0) == v.stride(0)
+    assert o.dtype == state.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, H * dv)
+    assert state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= H * dk * dv
+    assert (decay_tokens is None) != (decay_heads is None)
+    assert decay_tokens is None or (decay_tokens.dtype == torch.float32 and decay_tokens.is_contiguous()
+                                    and decay_tokens.shape == (T, H * dk))
+    assert decay_heads is None or (decay_heads.dtype == torch.float32 and decay_heads.numel() == H)
+    assert bonus is None or (bonus.dtype == r.dtype and bonus.is_contiguous() and bonus.numel() == H * dk)
+    call("nhv_decay_scan", dtype_code(r), o.data_ptr(), r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0),
+         _ptr(decay_tokens), _ptr(decay_heads), _ptr(bonus), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(),
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, dk, dv, int(bool(silu)),
+         int(bool(read_after)), stream_ptr())
+
+
 def relu_squared(x) -> None:
     """x = max(x, 0) ** 2 in place."""
     _need_cuda(x)
@@ -497,19 +589,22 @@ def mlstm_scan(y, proj, gates, gate_bias, cap: float, state, batch, H: int, d: i
          batch.state_slots.data_ptr(), batch.n_seqs, T, H, d, dv, MLSTM_LANES, stream_ptr())
 
 
-def moe_route(ids, weights, logits, correction, n_outputs: int, n_groups: int, keep: int) -> None:
+def moe_route(ids, weights, logits, correction, n_outputs: int, n_groups: int, keep: int, scores: str = "softmax",
+              renorm: bool = True) -> None:
     """The router's choice per token.  logits [T, >= n_outputs] float32 (a view with unit column stride; further columns
     are not read), correction [n_outputs] float32 or None -> ids [T, top] int32 and weights [T, top] float32.
     Scores are the softmax over all outputs; the choice is by score + correction among the outputs of the ``keep`` best
     of ``n_groups`` groups of neighbours (a group's score: its largest choice score); the weights are the chosen scores
-    divided by their sum (+ 1e-20)."""
+    divided by their sum (+ 1e-20).  ``scores`` "sigmoid": each output's score is the sigmoid of its logit;
+    ``renorm`` False: the weights are the chosen scores as they are."""
+    assert scores in ("softmax", "sigmoid")
     _need_cuda(ids, weights, logits, correction)
     T, top = ids.shape
     assert ids.dtype == torch.int32 and weights.dtype == logits.dtype == torch.float32 and weights.shape == ids.shape
     assert ids.is_contiguous() and weights.is_contiguous() and logits.stride(1) == 1 and logits.shape[0] == T
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n_outputs)
     call("nhv_moe_route", ids.data_ptr(), weights.data_ptr(), logits.data_ptr(), logits.stride(0), _ptr(correction), T,
-         n_outputs, n_groups, keep, top, stream_ptr())
+         n_outputs, n_groups, keep, top, int(scores == "sigmoid"), int(bool(renorm)), stream_ptr())
 
 
 MOE_TILE_SIMT = 16      # rows of one expert that a block of the CUDA-core products takes (MG_BM of csrc/moe.cu)
@@ -535,7 +630,8 @@ def moe_align(ids, n_experts: int, tile: int):
     return sorted_slots, slot_pos, tile_expert
 
 
-def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: int, limit: float, alpha: float) -> None:
+def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: int, limit: float, alpha: float,
+                     up_shift: float = 1.0, row_scale=None) -> None:
     """The experts' two products over the ordered rows on the CUDA cores, for any storage type and size, in a fixed order
     of summation: act [rows, ff] = glu(x[token] gate[e]^T, x[token] up[e]^T), y [rows, width] = act down[e]^T, with
     gate / up [E, ff, width] and down [E, width, ff]."""
@@ -549,9 +645,10 @@ def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: 
     tiles = tile_expert.numel()
     assert tiles * MOE_TILE_SIMT == sorted_slots.numel()
     call("nhv_moe_gemm_simt", dtype_code(x), 1, act.data_ptr(), x.data_ptr(), width, gate.data_ptr(), up.data_ptr(),
-         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), stream_ptr())
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), float(up_shift),
+         _ptr(row_scale), stream_ptr())
     call("nhv_moe_gemm_simt", dtype_code(x), 0, y.data_ptr(), act.data_ptr(), ff, down.data_ptr(), None,
-         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, stream_ptr())
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, 0.0, None, stream_ptr())
 
 
 MOE_ON_TENSOR_CORES = True      # tests switch it off to compare with the CUDA-core products at the same shapes
@@ -560,27 +657,30 @@ MOE_TCGEN05 = None              # the tcgen05 products: None where an expert see
 MOE_TCGEN05_TILE = 128          # rows per tile of the tcgen05 products (ROWS of csrc/moe_tcgen05.cu)
 
 
-def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
+def moe_experts(x, gate, up, down, ids, limit: float, alpha: float, up_shift: float = 1.0, row_scale=None):
     """Every chosen expert's output for every token: orders the slots of ids [T, top] by expert and runs the experts' two
     products over that order: bfloat16 with sizes in steps of 8 on the tensor cores (tcgen05 with tiles of 128 rows
     where an expert sees about a hundred rows or more; mma.sync with tiles of 64 rows below that and of 16 where it
     sees few and the products stream the weights), everything else on the CUDA cores.
+    The experts' unit is g' sigmoid(alpha g') (u' + up_shift) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+    (limit inf, alpha 1, up_shift 0: silu(g) u).  ``row_scale`` [T, top] float32: a factor on each chosen expert's input.
     Returns (y [rows, width], one row per slot that chose a real expert, and slot_pos [T * top] int32, the row of each
     slot or -1)."""
     E, ff, width = gate.shape
+    assert row_scale is None or (row_scale.dtype == torch.float32 and row_scale.is_contiguous() and row_scale.numel() == ids.numel())
     top = ids.shape[1]
     mma = MOE_ON_TENSOR_CORES and x.dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0
     tile = MOE_TILE_SIMT
     if mma:
         tile = MOE_TILE or (128 if ids.numel() >= 192 * E else 64 if ids.numel() >= 24 * E else 16)
     if mma and (MOE_TCGEN05 or (MOE_TCGEN05 is None and not MOE_TILE and ids.numel() >= 96 * E)):
-        return _moe_experts_tcgen05(x, gate, up, down, ids, limit, alpha)
+        return _moe_experts_tcgen05(x, gate, up, down, ids, limit, alpha, up_shift, row_scale)
     sorted_slots, slot_pos, tile_expert = moe_align(ids, E, tile)
     rows = sorted_slots.numel()
     act = torch.empty(rows, ff, dtype=x.dtype, device=x.device)
     y = torch.empty(rows, width, dtype=x.dtype, device=x.device)
     if not mma:
-        moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top, limit, alpha)
+        moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top, limit, alpha, up_shift, row_scale)
         return y, slot_pos
     _need_cuda(x, gate, up, down, ids)
     for name, t in (("x", x), ("gate", gate), ("up", up), ("down", down)):
@@ -589,13 +689,14 @@ def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
     assert gate.dtype == up.dtype == down.dtype == torch.bfloat16
     tiles = tile_expert.numel()
     call("nhv_moe_gemm_mma", tile, 1, act.data_ptr(), x.data_ptr(), width, gate.data_ptr(), up.data_ptr(),
-         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), stream_ptr())
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), float(up_shift),
+         _ptr(row_scale), stream_ptr())
     call("nhv_moe_gemm_mma", tile, 0, y.data_ptr(), act.data_ptr(), ff, down.data_ptr(), None,
-         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, stream_ptr())
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, 0.0, None, stream_ptr())
     return y, slot_pos
 
 
-def _moe_experts_tcgen05(x, gate, up, down, ids, limit: float, alpha: float):
+def _moe_experts_tcgen05(x, gate, up, down, ids, limit: float, alpha: float, up_shift: float = 1.0, row_scale=None):
     """``moe_experts`` for prompts in bfloat16: tiles of 128 rows per expert, the tokens' rows gathered into that order
     (so that a tile is one TMA box), both products with tcgen05.mma and tensor-memory accumulators."""
     _need_cuda(x, gate, up, down, ids)
@@ -612,16 +713,16 @@ def _moe_experts_tcgen05(x, gate, up, down, ids, limit: float, alpha: float):
     y = torch.empty(rows, width, dtype=x.dtype, device=x.device)
     call("nhv_moe_gather_rows", xs.data_ptr(), x.data_ptr(), sorted_slots.data_ptr(), rows, top, width, stream_ptr())
     call("nhv_moe_gemm_tcgen05", 1, act.data_ptr(), xs.data_ptr(), gate.data_ptr(), up.data_ptr(), E, sorted_slots.data_ptr(),
-         tile_expert.data_ptr(), tiles, ff, width, float(limit), float(alpha), stream_ptr())
+         tile_expert.data_ptr(), tiles, ff, width, float(limit), float(alpha), float(up_shift), _ptr(row_scale), stream_ptr())
     call("nhv_moe_gemm_tcgen05", 0, y.data_ptr(), act.data_ptr(), down.data_ptr(), None, E, sorted_slots.data_ptr(),
-         tile_expert.data_ptr(), tiles, width, ff, 0.0, 0.0, stream_ptr())
+         tile_expert.data_ptr(), tiles, width, ff, 0.0, 0.0, 0.0, None, stream_ptr())
     return y, slot_pos
 
 
 def moe_combine(out, y, x, ids, weights, slot_pos, n_experts: int, shared=None, shared_gate=None) -> None:
     """out[t] = sum over the token's choices of weight * (the expert's row of y, or x[t] itself for an identity expert)
     (+ sigmoid(shared_gate[t]) * shared[t]; a shared term without a gate counts fully).  ``shared_gate``: a float32
-    column view (one number per token)."""
+    column view (one number per token).  ``weights`` None: every choice counts fully."""
     _need_cuda(out, y, x, ids, weights, slot_pos, shared, shared_gate)
     _contig("out", out); _contig("y", y); _contig("x", x)
     T, width = x.shape
@@ -630,19 +731,21 @@ def moe_combine(out, y, x, ids, weights, slot_pos, n_experts: int, shared=None, 
     assert shared is None or (shared.shape == x.shape and shared.dtype == x.dtype and shared.is_contiguous())
     assert shared_gate is None or (shared is not None and shared_gate.dtype == torch.float32 and shared_gate.shape[0] == T)
     call("nhv_moe_combine", dtype_code(out), out.data_ptr(), y.data_ptr(), x.data_ptr(), _ptr(shared), _ptr(shared_gate),
-         0 if shared_gate is None else shared_gate.stride(0), ids.data_ptr(), weights.data_ptr(), slot_pos.data_ptr(), T, top,
+         0 if shared_gate is None else shared_gate.stride(0), ids.data_ptr(), _ptr(weights), slot_pos.data_ptr(), T, top,
          n_experts, width, stream_ptr())
 
 
 def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rotary_dim: int, nq: int, nkv: int, dk: int,
                     dv: int, eps: float | None, bias=None, values_from_keys: bool = False, q_weight=None,
-                    k_weight=None) -> None:
+                    k_weight=None, norm_first: bool = False, interleaved: bool = False) -> None:
     """qkv [T, nq*dk + nkv*dk + nkv*dv] -> q_out [T, nq*dk] (rotated, then scaled to unit root mean square; eps None:
     no norm) and K / V rows in kv_pages [pages, 2, nkv, page_size, row] at slot_mapping.  kv_pages None: queries only.
     ``bias`` (one element per query and key column of qkv, in its type) is added in 32-bit before the rotation.
     ``values_from_keys``: the stored values are the key heads as projected (bias added, not rotated); qkv then ends
     with the keys (it may have further columns that this op does not read) and dv == dk.  ``q_weight`` / ``k_weight``
-    [dk]: the normed query / key heads times this weight (one weight for all heads of a kind)."""
+    [dk]: the normed query / key heads times this weight (one weight for all heads of a kind).  ``norm_first``: the
+    norm and its weight come before the rotation.  ``interleaved``: element 2i turns with element 2i + 1 instead of
+    element i with element i + rotary_dim / 2 (the table is the same)."""
     _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, bias, q_weight, k_weight)
     for hw in (q_weight, k_weight):
         assert hw is None or (hw.dtype == qkv.dtype and hw.is_contiguous() and hw.numel() == dk and eps is not None)
@@ -663,11 +766,12 @@ def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rota
          _ptr(kv_pages), _ptr(slot_mapping), _ptr(positions), _ptr(cos_sin), int(rotary_dim),
          0 if cos_sin is None else cos_sin.shape[0], n_tokens, nq, nkv, dk, dv, row, page_size, n_pages,
          -1.0 if eps is None else float(eps), _ptr(bias), int(bool(values_from_keys)), _ptr(q_weight), _ptr(k_weight),
-         stream_ptr())
+         int(bool(norm_first)), int(bool(interleaved)), stream_ptr())
 
 
 def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_tokens: int, nq: int, nkv: int,
-                        dk: int, dv: int, scale: float, sinks=None, window: int = 0, chunk: int = 0, slopes=None) -> None:
+                        dk: int, dv: int, scale: float, sinks=None, window: int = 0, chunk: int = 0, slopes=None,
+                        keep_first: int = 0) -> None:
     """Causal attention of this step's tokens over the pages with key heads of dk and value heads of dv elements:
     q [T, nq*dk] -> out [T, nq*dv].  ``sinks`` [nq] float32: a term exp(sink) in each head's softmax denominator.
     ``window`` > 0: the last ``window`` keys only; ``chunk`` > 0: only the keys of the query's own chunk of ``chunk``
@@ -685,25 +789,25 @@ def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int
     call("nhv_attention_simt_ex", dtype_code(q), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
          kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(),
          n_seqs, n_tokens, nq, nkv, dk, dv, row, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks),
-         _ptr(slopes), planes, stream_ptr())
+         _ptr(slopes), planes, int(keep_first), stream_ptr())
 
 
 SINK_ATTENTION_ON_TENSOR_CORES = True     # tests switch it off to compare with the CUDA-core kernel at the same shapes
 
 
 def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, dv: int, scale: float, sinks=None,
-                   window: int = 0, chunk: int = 0, slopes=None) -> None:
+                   window: int = 0, chunk: int = 0, slopes=None, keep_first: int = 0) -> None:
     """Attention of the step's tokens over the cache for layers with a sink and / or value heads of another size
     than their key heads: picks the kernel for the dtype and sizes.  bfloat16 with key and value heads of one size
     (in steps of 16) runs on the tensor cores like ``attention``; float32 and unequal head sizes on the CUDA cores."""
     if (SINK_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and kv_pages.shape[-1] == dk
-            and kv_pages.shape[1] == 2 and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
+            and kv_pages.shape[1] == 2 and keep_first == 0 and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
         attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
                               batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
                               nq, nkv, dk, scale, window, sinks, chunk, slopes)
         return
     attention_sink_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
-                        nq, nkv, dk, dv, scale, sinks, window, chunk, slopes)
+                        nq, nkv, dk, dv, scale, sinks, window, chunk, slopes, keep_first)
 
 
 def linear_f32(out, x, weight) -> None:

@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import ginodra, muvonex, nomudra, qwen3  # noqa: F401
+from . import beputar, ginodra, muvonex, nomudra, qwen3  # noqa: F401

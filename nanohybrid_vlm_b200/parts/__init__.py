@@ -1,4 +1,4 @@
-from . import (attention, block, delta_rule, embedding, feed_forward, input_filter, latent_attention, mlstm, moe, norm,  # noqa: F401
+from . import (attention, block, delta_rule, embedding, feed_forward, input_filter, latent_attention, linear_recurrence, mlstm, moe, norm,  # noqa: F401
                parallel_mixer, position, sink_attention, state_space)    # (importing registers the built-in parts)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, FILTERS, HEADS, MIXERS, NORMS, POSITIONS, Block, InputFilter, SharedPagesNeed, BuildEnv, CacheView, CompositeNeed,
                    Embedding,

@@ -54,7 +54,7 @@ BLOCKS = Registry("block arrangement")
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every token (or of the last ``window`` tokens, or of the current chunk of ``chunk``
-    positions) in pages.  ``v_head_dim``: the size of a value head where it differs from a key head's; a page row then
+    positions) in pages.  ``keep_first``: with a window, the keys of the first ``keep_first`` positions stay as well.  ``v_head_dim``: the size of a value head where it differs from a key head's; a page row then
     has room for the larger of the two and each kind uses its leading elements.  ``planes``: 2 for a key and a value
     plane per page; 1 for pages that hold one row per token and head (a latent vector that is key and value at once)."""
     num_kv_heads: int
@@ -63,6 +63,7 @@ class PagedKVNeed:
     v_head_dim: int | None = None
     chunk: int | None = None
     planes: int = 2
+    keep_first: int = 0
 
     @property
     def row_dim(self) -> int:
@@ -174,9 +175,12 @@ class Pending:
     next norm.  Blocks that keep their stream in float32 hand this on in place of a hidden tensor.
     ``post``: a norm that the (single) term still has to pass before it is added (blocks that norm a sub-block's
     output as well as its input); the next norm applies it inside its own kernel where it can, else through
-    :meth:`settled`."""
+    :meth:`settled`.
+    ``rounded``: the stream itself rounded to the model's type, where the block before has it at hand (nothing pending);
+    a block whose sub-blocks read the stream unnormed takes it from here instead of rounding the stream again."""
     terms: tuple = ()
     post: "Norm | None" = None
+    rounded: "torch.Tensor | None" = None
 
     def settled(self) -> "Pending":
         """The same sum with ``post`` applied by that norm's own ``forward`` (rounded to the model's type)."""
@@ -190,6 +194,12 @@ class Mixer(Part):
         """The mixer's output as a weighted sum ((tensor, coef), ...) that the caller may add term by term in 32-bit
         instead of receiving one rounded tensor.  Default: the one tensor of ``forward``."""
         return ((self.forward(x, batch, cache), 1.0),)
+
+    def forward_normed_terms(self, x: torch.Tensor, batch, cache: "CacheView") -> tuple:
+        """The mixer's output as ((tensor, coef, weight or None), ...): a weighted sum whose terms may each still have to
+        pass an RMS norm over the model width with that weight (eps: ``self.side_eps``).  A block that norms the mixer's
+        output anyway does these norms in the same kernel.  Default: the terms of ``forward_terms``, no norms."""
+        return tuple((t, c, None) for t, c in self.forward_terms(x, batch, cache))
 
     def cache_need(self) -> "PagedKVNeed | FixedStateNeed | CompositeNeed | None":
         return None
@@ -215,6 +225,11 @@ class Norm(Part):
 
     def forward_add_rows(self, x: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Norm of (x + residual) at the given rows only; nothing is written back."""
+        raise NotImplementedError
+
+    def add_normed(self, terms: tuple, residual: torch.Tensor, side_eps=None, want_rounded: bool = True):
+        """residual (float32, in place) += norm(sum of ``terms``), terms as ``Mixer.forward_normed_terms`` gives them: for
+        blocks that norm a sub-block's output.  Returns the new stream rounded to the model's type (or None)."""
         raise NotImplementedError
 
 

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, FILTERS, MIXERS, NORMS, Block, CompositeNeed, Pending
 
 
@@ -105,6 +106,42 @@ class SandwichResidualBlock(Block):
         return pending, residual
 
 
+class PostNormResidualBlock(Block):
+    """A norm on each sub-block's output only: x <- x + post1(mixer(x)), then x <- x + post2(ffn(x)).  The sub-blocks
+    read the stream x itself (rounded to the model's type); the stream is kept in float32.  Each norm (``mixer_norm``,
+    ``ffn_norm``) norms its sub-block's output, multiplies it by its weight and, if it has one, by its scale per channel
+    (``post_scale``), and adds the result onto the stream in one kernel (``Norm.add_normed``) that also hands back the
+    new stream rounded, which the next sub-block reads.  A mixer whose output is a sum of terms that each pass a norm of
+    their own (``forward_normed_terms``) has those norms done in the same kernel.  A layer may have no feed-forward
+    (then also no second norm).  The block hands on an empty :class:`Pending` that carries the rounded stream."""
+    OPTIONAL = ("ffn", "ffn_norm")
+
+    def __init__(self, spec, parts):
+        super().__init__(spec, parts)
+        if ("ffn" in parts) != ("ffn_norm" in parts):
+            raise ValueError("a feed-forward comes with its norm, or not at all")
+
+    def forward(self, hidden, residual, batch, cache):
+        if residual is None:
+            residual = hidden if hidden.dtype == torch.float32 else hidden.float()
+            hidden = Pending()
+        if not isinstance(hidden, Pending) or hidden.terms:
+            raise TypeError("this block follows blocks that leave nothing pending on a float32 stream")
+        exact = self.mixer.env.dtype == torch.float32       # the stream itself is what the sub-blocks read
+        x = residual if exact else hidden.rounded
+        if x is None:
+            x = self.mixer.new(*residual.shape)
+            ops.stream_round(x, residual)
+        terms = self.mixer.forward_normed_terms(x, batch, cache)
+        x = self.mixer_norm.add_normed(terms, residual, getattr(self.mixer, "side_eps", None), want_rounded=not exact)
+        ffn = self.parts.get("ffn")
+        if ffn is not None:
+            m = ffn.forward(residual if exact else x, batch)
+            x = self.ffn_norm.add_normed(((m, 1.0, None),), residual, want_rounded=not exact)
+        return Pending(rounded=x), residual
+
+
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+BLOCKS.register("postnorm_residual", PostNormResidualBlock)
 BLOCKS.register("sandwich_residual", SandwichResidualBlock)
 BLOCKS.register("parallel_residual", ParallelResidualBlock)

@@ -76,9 +76,9 @@ class GatedMLP(FeedForward):
 
 class DenseMLP(FeedForward):
     """down(act(up(x))): a feed-forward without a gate.  Parameters: ``intermediate_size``, ``activation`` ("relu2": the
-    square of relu), ``names`` (the checkpoint's names of the two matrices; default ("up", "down")).  Tensors: ``up``
+    square of relu; "gelu_tanh": the tanh form of GELU), ``names`` (the checkpoint's names of the two matrices; default ("up", "down")).  Tensors: ``up``
     [I, width], ``down`` [width, I]."""
-    ACTIVATIONS = {"relu2": "relu_squared"}
+    ACTIVATIONS = {"relu2": "relu_squared", "gelu_tanh": "gelu_tanh"}
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -11,7 +11,12 @@ included, form ``groups`` equal groups of neighbours and only the ``keep`` best 
 score is its largest choice score), ``correction`` (True: a learned vector ``correction`` is added to the scores for
 the choice only), ``intermediate_size`` / ``limit`` / ``alpha`` (of every expert, a clamped gated unit), ``shared`` (a
 PartSpec of a feed-forward that every token passes, its tensors under ``shared.``; None: none), ``shared_gate`` (True:
-the shared output is multiplied by sigmoid(sg(x)), one number per token, ``shared.sg`` [1, width]).
+the shared output is multiplied by sigmoid(sg(x)), one number per token, ``shared.sg`` [1, width]), ``scores``
+("softmax", the default, or "sigmoid": each output's score is the sigmoid of its own logit), ``renorm`` (True: the chosen
+scores are divided by their sum; False: they are the weights as they are), ``weight_on`` ("output", the default: a
+chosen expert's output is multiplied by its weight; "input": its input is, out = sum of expert(w * x)), ``limit`` None
+(no clamp) and ``up_shift`` (what is added to the up half, 1 unless given): limit None, alpha 1, up_shift 0 make the
+experts plain gated units, down(silu(gate x) * (up x)).
 
 Router: z = router(x) with 32-bit sums; s = softmax(z) over all outputs; choice by s + correction; the weights of the
 chosen are their s divided by the sum of the chosen s (+ 1e-20).  The output is the weighted sum of the chosen experts'
@@ -75,8 +80,17 @@ class RoutedMoE(FeedForward):
         self.keep = int(spec.get("keep", self.groups))
         self.N = self.E + self.I0
         self.inter = int(spec["intermediate_size"])
-        self.limit = float(spec["limit"])
+        limit = spec.get("limit")
+        self.limit = float("inf") if limit is None else float(limit)
         self.alpha = float(spec.get("alpha", 1.702))
+        self.up_shift = float(spec.get("up_shift", 1.0))
+        self.scores = spec.get("scores", "softmax")
+        self.renorm = bool(spec.get("renorm", True))
+        self.weight_on = spec.get("weight_on", "output")
+        if self.scores not in ("softmax", "sigmoid") or self.weight_on not in ("output", "input"):
+            raise ValueError(f"unknown router scores {self.scores!r} or weight_on {self.weight_on!r}")
+        if self.weight_on == "input" and self.I0:
+            raise ValueError("identity experts are not offered with weights on the experts' inputs")
         self.has_correction = bool(spec.get("correction", True))
         if self.E <= 0 or self.I0 < 0 or not 0 < self.top <= self.N:
             raise ValueError(f"{self.E} experts, {self.I0} identity experts, top {self.top}: not a router")
@@ -122,11 +136,15 @@ class RoutedMoE(FeedForward):
         ops.linear_f32(logits, x, self.w_router)
         ids = self.new(T, self.top, dtype=torch.int32)
         weights = self.new(T, self.top, dtype=torch.float32)
-        ops.moe_route(ids, weights, logits, self.w_correction if self.has_correction else None, self.N, self.groups, self.keep)
-        y, slot_pos = ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, self.limit, self.alpha)
+        ops.moe_route(ids, weights, logits, self.w_correction if self.has_correction else None, self.N, self.groups, self.keep,
+                      scores=self.scores, renorm=self.renorm)
+        on_input = self.weight_on == "input"
+        # a weight on an expert's input is a factor on the 32-bit sums of its two first products
+        y, slot_pos = ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, self.limit, self.alpha, self.up_shift,
+                                      weights if on_input else None)
         shared = self.shared.forward(x, batch) if self.shared is not None else None
         out = self.new(T, W)
-        ops.moe_combine(out, y, x, ids, weights, slot_pos, self.E, shared,
+        ops.moe_combine(out, y, x, ids, None if on_input else weights, slot_pos, self.E, shared,
                         logits[:, self.N] if self.shared_gate else None)
         return out
 

@@ -3,7 +3,9 @@
 Parameters: ``width``, ``eps``, ``weight_offset`` (0 for ``x * w``; 1 for the ``x * (1 + w)``
 convention some models store), ``source`` (the checkpoint's name of the weight, default "weight"), ``groups`` (the
 row is cut into this many equal consecutive parts and each is divided by the root mean square of its own elements;
-default 1; over a float32 stream only).
+default 1; over a float32 stream only), ``post_scale`` (the checkpoint's name of a second vector [width] that multiplies
+the normed output after the weight, a scale per channel on a sub-block's contribution; only where the norm adds a
+sub-block's output onto a float32 stream, ``add_normed``).
 
 Over a residual stream kept in float32 (``forward_add`` / ``forward_add_rows`` given a :class:`Pending`) the terms
 are added in 32-bit, the statistics and the product with the weight are 32-bit, and the result is rounded once.
@@ -27,14 +29,36 @@ class RMSNorm(Norm):
         self.groups = int(spec.get("groups", 1))
         if self.groups < 1 or self.width % self.groups:
             raise ValueError(f"a norm over {self.width} elements does not divide into {self.groups} parts")
+        self.post_scale = spec.get("post_scale")
 
     def _plain_only(self):
         if self.groups != 1:
             raise TypeError("a norm in groups works over a float32 residual stream: it takes a Pending")
+        if self.post_scale is not None:
+            raise TypeError("a norm with a scale per channel adds a sub-block's output onto a float32 stream (add_normed)")
 
     def params(self):
-        return [ParamDecl("weight", (self.width,), init="norm" if self.weight_offset == 0.0 else "zeros_noise",
-                          sources=(Source(self.source, 0, self.width),))]
+        # the tensors carry the checkpoint's names where a scale comes with the norm, so that two such norms can share
+        # a layer's prefix
+        name = "weight" if self.post_scale is None else self.source
+        decls = [ParamDecl(name, (self.width,), init="norm" if self.weight_offset == 0.0 else "zeros_noise",
+                           sources=(Source(self.source, 0, self.width),))]
+        if self.post_scale is not None:
+            decls.append(ParamDecl(self.post_scale, (self.width,), init="layer_scale",
+                                   sources=(Source(self.post_scale, 0, self.width),)))
+        return decls
+
+    def bind(self, tensors):
+        if self.post_scale is None:
+            return super().bind(tensors)
+        self.w_weight, self.w_post_scale = tensors[self.source], tensors[self.post_scale]
+
+    def add_normed(self, terms, residual, side_eps=None, want_rounded=True):
+        if self.groups != 1 or self.weight_offset != 0.0:
+            raise TypeError("the output norm is a plain RMS norm (one group, the weight as it is stored)")
+        rounded = self.new(*residual.shape) if want_rounded else None
+        ops.postnorm_stream(residual, rounded, terms, self.w_weight, getattr(self, "w_post_scale", None), self.eps, side_eps)
+        return rounded
 
     def forward(self, x):
         self._plain_only()
@@ -44,6 +68,8 @@ class RMSNorm(Norm):
 
     def forward_add(self, x, residual):
         if isinstance(x, Pending):
+            if self.post_scale is not None:
+                self._plain_only()
             x = x.settled()
             out = self.new(*residual.shape)
             ops.rmsnorm_stream(out, residual, self.w_weight, self.eps, addends=x.terms, weight_offset=self.weight_offset,

@@ -17,7 +17,13 @@ q and k head is multiplied by a learned weight [head_dim], ``q.norm`` / ``k.norm
 ``distance_slope_base`` (None, or b: the score of head h at distance n behind the query loses 2^(-b (h + 1) / H) * n),
 ``own_kv`` (False: the layer has no key / value projections, norms or pages of its own and reads the keys and values
 that another run stored, ``LayerRun.cache_from``), ``keep_window`` (how many keys the pages keep, where that is more
-than this layer's own ``window`` shows: a layer whose pages another layer with a wider window reads; None: all).
+than this layer's own ``window`` shows: a layer whose pages another layer with a wider window reads; None: all),
+``keep_first`` (n, with a window: the keys at positions below n stay visible to every later query, at their true
+positions, and their pages are kept), ``sink_constant`` (a number: the denominator of every head holds exp of it, as a
+learned sink would, but no tensor is read; 0.0 adds one), ``qk_norm_order`` ("after_rotation", the default, or
+"before_rotation": the unit norm and its weight come before the rotation), ``rope_layout`` ("half": element i turns
+with element i + dims / 2, the default; "interleaved": element 2i with element 2i + 1), ``bias`` may also be "qk":
+biases on q and k only.
 
 Tensors: ``qkv`` [(nq + nkv) d (+ nkv dv) (+ nq dv), width], rows q then k then v then g, packed from the
 checkpoint's ``q``, ``k``, ``v``, ``g`` (those that exist); ``qk_bias`` [(nq + nkv) d] from ``q.b``, ``k.b``; ``sink``
@@ -44,17 +50,32 @@ class SinkAttention(Mixer):
         eps = spec.get("unit_norm_eps")
         self.eps = None if eps is None else float(eps)
         self.has_sink = bool(spec.get("sink", True))
+        self.sink_constant = spec.get("sink_constant")
+        if self.sink_constant is not None:
+            if spec.get("sink", False):
+                raise ValueError("a sink is learned (sink=True) or a constant (sink_constant), not both")
+            import torch
+            self.has_sink = False
+            self.fixed_sinks = torch.full((self.nq,), float(self.sink_constant), dtype=torch.float32, device=env.device)
+        self.keep_first = int(spec.get("keep_first", 0) or 0)
+        self.norm_order = spec.get("qk_norm_order", "after_rotation")
+        self.rope_layout = spec.get("rope_layout", "half")
+        if self.norm_order not in ("after_rotation", "before_rotation") or self.rope_layout not in ("half", "interleaved"):
+            raise ValueError(f"unknown qk_norm_order {self.norm_order!r} or rope_layout {self.rope_layout!r}")
         self.window = spec.get("window")
         self.keep_window = spec.get("keep_window", self.window)
         if self.keep_window is not None and (self.window is None or self.keep_window < self.window):
             raise ValueError("the pages must keep at least the keys that the layer's window shows")
         self.chunk = spec.get("chunk")
+        if self.keep_first and (self.window is None or self.keep_window != self.window):
+            raise ValueError("kept first keys go with a window of the layer's own")
         self.values = spec.get("values", "projected")
         if self.values not in ("projected", "keys"):
             raise ValueError(f"values are 'projected' or 'keys', not {self.values!r}")
         if self.values == "keys" and self.dv != self.d:
             raise ValueError(f"values that are the keys have the keys' size {self.d}, not {self.dv}")
         self.bias = bool(spec.get("bias", False))
+        self.out_bias = self.bias and spec.get("bias") != "qk"
         self.gate = spec.get("output_gate")
         if self.gate not in (None, "sigmoid", "sigmoid_head"):
             raise ValueError(f"an output gate is None, 'sigmoid' or 'sigmoid_head', not {self.gate!r}")
@@ -96,13 +117,15 @@ class SinkAttention(Mixer):
         if self.bias:
             if not self.own_kv:
                 raise ValueError("projection biases are not offered for a layer without keys of its own")
-            decls += [ParamDecl("qk_bias", (self.q_size + self.k_size,), init="zeros_noise",
-                                sources=(Source("q.b", 0, self.q_size), Source("k.b", self.q_size, self.k_size))),
-                      ParamDecl("o.b", (H,), init="zeros_noise")]
+            decls.append(ParamDecl("qk_bias", (self.q_size + self.k_size,), init="zeros_noise",
+                                   sources=(Source("q.b", 0, self.q_size), Source("k.b", self.q_size, self.k_size))))
+            if self.out_bias:
+                decls.append(ParamDecl("o.b", (H,), init="zeros_noise"))
         return decls
 
     def cache_need(self):
-        return PagedKVNeed(self.nkv, self.d, self.keep_window, v_head_dim=self.dv, chunk=self.chunk)
+        return PagedKVNeed(self.nkv, self.d, self.keep_window, v_head_dim=self.dv, chunk=self.chunk,
+                           keep_first=self.keep_first)
 
     def streamed_weights(self):
         return [(self.w_qkv, 0), (self.w_o, 0)]
@@ -120,17 +143,19 @@ class SinkAttention(Mixer):
                             table, rotary_dim, self.nq, self.nkv, self.d, self.dv, self.eps,
                             bias=self.w_qk_bias if self.bias else None, values_from_keys=self.values == "keys",
                             q_weight=self.w_q_norm if self.norm_weight else None,
-                            k_weight=self.w_k_norm if self.norm_weight and self.own_kv else None)
+                            k_weight=self.w_k_norm if self.norm_weight and self.own_kv else None,
+                            norm_first=self.norm_order == "before_rotation", interleaved=self.rope_layout == "interleaved")
         o = self.new(T, self.nq * self.dv)
         ops.attention_sink(o, q, cache.pages, cache.tables, batch, self.nq, self.nkv, self.d, self.dv, self.scale,
-                           self.w_sink if self.has_sink else None, self.window or 0, self.chunk or 0, self.slopes)
+                           self.w_sink if self.has_sink else getattr(self, "fixed_sinks", None), self.window or 0,
+                           self.chunk or 0, self.slopes, self.keep_first)
         if self.gate == "sigmoid_head":
             ops.sigmoid_mul_heads(o, o, qkv[:, self.q_size + self.k_size + self.v_size:], self.dv)
         elif self.gate:
             ops.sigmoid_mul(o, o, qkv[:, self.q_size + self.k_size + self.v_size:])
         y = self.new(T, self.env.hidden_size)
         ops.linear(y, o, self.w_o)
-        if self.bias:
+        if self.out_bias:
             ops.add_row_bias(y, self.w_o_b)
         return y
 

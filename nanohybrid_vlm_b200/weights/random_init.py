@@ -39,7 +39,9 @@ INITS = {
     "dyntanh_alpha": _normal(0.05, 0.5),        # the scalar of a Dynamic Tanh norm
     "gate_bias": _normal(1.0),                  # biases of recurrent gates: spread, so that decays differ
     "filter_taps": _normal(0.3),                # short filters over time: large enough to show in the output
-    "unit": _normal(1.0),                       # small inner matrices whose input is bounded (a tanh)
+    "unit": _normal(1.0),
+    "layer_scale": _normal(0.1, 0.5),
+    "mix_share": _normal(0.2, 0.5),             # how much of the token before enters a mix           # a scale per channel on a sub-block's contribution                       # small inner matrices whose input is bounded (a tanh)
     "zeros": lambda shape, gen, device: torch.zeros(shape, dtype=torch.float32, device=device),
 }
 
