@@ -6,6 +6,7 @@
     python bench.py --designs                Muvonex beside a Qwen3 of equal size (prefill, decode, time by kind of kernel)
     python bench.py --designs nomudra        Nomudra beside a Muvonex of equal active size, the same way
     python bench.py --designs ginodra        Ginodra beside a Muvonex of equal size, the same way
+    python bench.py --designs beputar        Beputar beside a Nomudra of the same width and expert sizes, the same way
 
 The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 layers, width 4096,
 32/8 heads of 128, feed-forward 12288, vocabulary 151936), bfloat16, random weights, batch 8,
@@ -702,6 +703,27 @@ def ginodra_config(width: int, heads: int, ff: int, layers: int) -> dict:
                 canon=dict(taps=3), logit_scale=1.0, logit_softcap=30.0, layers=out, dtype="bfloat16")
 
 
+def beputar_config(width: int, heads: int, ff: int, layers: int) -> dict:
+    """In turn: attention that keeps its first 4 keys beside a window of 1,024 (a quarter as many key heads, rotation of
+    half of each head) next to linear attention with a constant decay per head (heads of 128); attention in a window of
+    4,096 with rescaled rotary frequencies; time mixing with heads of 64 and a decay projection of rank 64; and the
+    pair again.  The first layer of every four has the dense feed-forward ``ff``; the others a mixture of 16 experts of
+    which a token uses 4, and a shared expert: together as wide as ``ff`` (4 * 2/11 + 3/11 of it)."""
+    moe = dict(kind="moe", router=dict(experts=16, top=4), expert=dict(ff=ff * 2 // 11), shared=dict(ff=ff * 3 // 11))
+    kv = max(heads // 4, 1)
+    pair = dict(type="parallel", mixer=dict(
+        left=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, rot=dict(base=500000.0, dims=64),
+                  mask=dict(size=1024, keep_first=4)),
+        right=dict(heads=heads // 2, dim=128, vdim=128, decay=[1.0 - 2.0 ** -(5 + 3 * h / max(heads // 2 - 1, 1)) for h in range(heads // 2)])))
+    attention = dict(type="attention", mixer=dict(
+        heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=4096),
+        rot=dict(base=50000.0, dims=128, scaling=dict(factor=4.0, original=1024, fast=32.0, slow=1.0))))
+    mixing = dict(type="wkv", mixer=dict(heads=width // 64, dim=64, decay_rank=64))
+    kinds = [dict(pair, mlp=dict(kind="dense", ff=ff)), dict(attention, mlp=moe), dict(mixing, mlp=moe), dict(pair, mlp=moe)]
+    return dict(architecture="Beputar", vocab=DESIGN_VOCAB, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-6),
+                layers=[kinds[i % 4] for i in range(layers)], dtype="bfloat16")
+
+
 def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weights: float) -> dict:
     """A Qwen3 of this width whose layers hold as many weights as ``layer_weights`` (the feed-forward takes up the
     difference, rounded to 256)."""
@@ -715,7 +737,8 @@ def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weight
 def bench_designs(args) -> dict:
     """Prefill and decode throughput of Muvonex beside a Qwen3 of equal size (``--designs``), or of Nomudra beside a
     Muvonex whose layers hold as many weights as a Nomudra token uses (``--designs nomudra``), or of Ginodra beside a
-    Muvonex of equal size (``--designs ginodra``), and the time of each kind
+    Muvonex of equal size (``--designs ginodra``), or of Beputar beside a Nomudra of the same width and expert sizes
+    (``--designs beputar``), and the time of each kind
     of kernel in a prefill step (CUDA events around every launch of an eager run) with its share of the measured
     roofline."""
     import torch
@@ -737,7 +760,8 @@ def bench_designs(args) -> dict:
              "moe_experts": "experts", "moe_combine": "experts_sum", "causal_filter_add": "short_conv",
              "latent_rope_store": "rope_store", "linear_heads": "gemm_heads", "attention_sink_simt": "attention",
              "latent_attention": "attention", "latent_expand": "attention", "general_delta": "delta_rule", "sigmoid_mul_heads": "act_mul",
-             "relu_squared": "act_mul", "scale_softcap": "act_mul"}
+             "relu_squared": "act_mul", "scale_softcap": "act_mul", "gelu_tanh": "act_mul", "postnorm_stream": "norm",
+             "stream_round": "norm", "token_shift_mix": "token_shift", "decay_scan": "decay_scan", "decay_lowrank": "decay_prep"}
     kinds = {k: v for k, v in kinds.items() if hasattr(ops, k)}
     stock = {name: getattr(ops, name) for name in kinds}
     gen = torch.Generator().manual_seed(SEED)
@@ -902,6 +926,11 @@ def bench_designs(args) -> dict:
             ff = max(256, int(round((sz["ff"] + (per_layer - m0 / layers) / (3 * sz["width"])) / 256)) * 256)
             results[name] = {"ginodra": g, "muvonex": run_one(muvonex_config(sz["width"], sz["heads"], ff, layers), DESIGN_VOCAB)}
             continue
+        if args.designs == "beputar":
+            # the same width, heads, expert count and expert sizes: both report the weights that a token uses
+            results[name] = {"beputar": run_one(beputar_config(sz["width"], sz["heads"], sz["ff"], layers), DESIGN_VOCAB),
+                             "nomudra": run_one(nomudra_config(sz["width"], sz["heads"], sz["ff"], layers), DESIGN_VOCAB)}
+            continue
         mcfg = muvonex_config(sz["width"], sz["heads"], sz["ff"], layers)
         m = run_one(mcfg, DESIGN_VOCAB)
         layer_weights = (m["weights_m"] * 1e6 - DESIGN_VOCAB * sz["width"]) / layers
@@ -933,7 +962,7 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
     ap.add_argument("--breakdown", action="store_true",
                     help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
-    ap.add_argument("--designs", nargs="?", const="muvonex", default=None, choices=["muvonex", "nomudra", "ginodra"],
+    ap.add_argument("--designs", nargs="?", const="muvonex", default=None, choices=["muvonex", "nomudra", "ginodra", "beputar"],
                     help="two designs side by side, prefill and decode throughput at a few layer sizes, one JSON line: "
                          "Muvonex beside a Qwen3 of equal size (the default), or Nomudra beside a Muvonex of equal active size")
     ap.add_argument("--design-size", default="all", choices=["all", *DESIGN_SIZES], help="one size of --designs")

@@ -159,36 +159,58 @@ NHV_API int nhv_decay_scan(int dtype, float* o, const void* r, const void* k, co
   return 0;
 }
 
+constexpr int DL_TOKENS = 16;       // tokens per block of decay_lowrank: a row of w2 is read once for all of them
+
 template <typename T>
 __global__ void decay_lowrank_kernel(float* __restrict__ w, const float* __restrict__ inner, int inner_stride,
                                      const T* __restrict__ w2, const T* __restrict__ w0, int n_tokens, int n, int rank) {
-  extern __shared__ float th[];                       // tanh of the token's inner projection
+  extern __shared__ float th[];                       // [DL_TOKENS][rank]: tanh of the tokens' inner projections
   pdl_prologue();
-  const int t = blockIdx.x;
-  for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(inner[(size_t)t * inner_stride + j]);
-  __syncthreads();
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
-    float z = to_f32<T>(w0[c]);
-    const T* row = w2 + (size_t)c * rank;
-    for (int j = 0; j < rank; ++j) z = fmaf(th[j], to_f32<T>(row[j]), z);
-    w[(size_t)t * n + c] = expf(-expf(z));
+  const int t0 = blockIdx.x * DL_TOKENS;
+  const int nt = min(DL_TOKENS, n_tokens - t0);
+  for (int i = threadIdx.x; i < nt * rank; i += blockDim.x) {
+    const int tt = i / rank, j = i - tt * rank;
+    th[i] = tanhf(inner[(size_t)(t0 + tt) * inner_stride + j]);
   }
+  __syncthreads();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  float z[DL_TOKENS];
+  const float z0 = to_f32<T>(w0[c]);
+#pragma unroll
+  for (int tt = 0; tt < DL_TOKENS; ++tt) z[tt] = z0;
+  const T* row = w2 + (size_t)c * rank;
+  for (int j = 0; j < rank; ++j) {                    // every token's sum runs over j in ascending order
+    const float wj = to_f32<T>(row[j]);
+#pragma unroll
+    for (int tt = 0; tt < DL_TOKENS; ++tt)
+      if (tt < nt) z[tt] = fmaf(th[tt * rank + j], wj, z[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < DL_TOKENS; ++tt)
+    if (tt < nt) w[(size_t)(t0 + tt) * n + c] = expf(-expf(z[tt]));
 }
 
 NHV_API int nhv_decay_lowrank(int dtype, float* w, const float* inner, int inner_stride, const void* w2, const void* w0,
                               int n_tokens, int n, int rank, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  NHV_REQUIRE(n > 0 && rank > 0 && rank <= 8192 && inner_stride >= rank, "decay_lowrank: bad sizes (n %d, rank %d)", n, rank);
+  NHV_REQUIRE(n > 0 && rank > 0 && rank <= 2048 && inner_stride >= rank, "decay_lowrank: bad sizes (n %d, rank %d)", n, rank);
   const int threads = 128;
-  dim3 grid(n_tokens, (n + threads - 1) / threads > 8 ? 8 : (n + threads - 1) / threads);
-  const size_t smem = (size_t)rank * sizeof(float);
-  if (dtype == NHV_F32)
-    nhv_launch(decay_lowrank_kernel<float>, grid, threads, smem, stream, w, inner, inner_stride, (const float*)w2,
-               (const float*)w0, n_tokens, n, rank);
-  else if (dtype == NHV_BF16)
-    nhv_launch(decay_lowrank_kernel<__nv_bfloat16>, grid, threads, smem, stream, w, inner, inner_stride,
-               (const __nv_bfloat16*)w2, (const __nv_bfloat16*)w0, n_tokens, n, rank);
+  dim3 grid((n_tokens + DL_TOKENS - 1) / DL_TOKENS, (n + threads - 1) / threads);
+  NHV_REQUIRE(grid.y <= 65535, "decay_lowrank: %d channels are beyond the grid's reach", n);
+  const size_t smem = (size_t)DL_TOKENS * rank * sizeof(float);
+#define LAUNCH(T)                                                                                                     \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      NHV_CUDA(cudaFuncSetAttribute(decay_lowrank_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
+               "decay_lowrank");                                                                                      \
+    nhv_launch(decay_lowrank_kernel<T>, grid, threads, smem, stream, w, inner, inner_stride, (const T*)w2,            \
+               (const T*)w0, n_tokens, n, rank);                                                                      \
+  } while (0)
+  if (dtype == NHV_F32) LAUNCH(float);
+  else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
   else NHV_REQUIRE(false, "decay_lowrank: unknown dtype %d", dtype);
+#undef LAUNCH
   NHV_CHECK_LAUNCH("decay_lowrank");
   return 0;
 }

@@ -135,7 +135,7 @@ struct RowState {
 template <int NT>
 __device__ __forceinline__ void warp_tile(RowState& st, const uint32_t (&qf)[KS][4], const bf16* ks, const bf16* vs,
                                           int kb, int key_base, const int (&row_lo)[2], const int (&row_hi)[2],
-                                          float scale_log2, const float (&row_slope)[2]) {
+                                          float scale_log2, const float (&row_slope)[2], int keep_first) {
   const int lane = threadIdx.x & 31;
   float s[NT][4];
 #pragma unroll
@@ -160,7 +160,7 @@ __device__ __forceinline__ void warp_tile(RowState& st, const uint32_t (&qf)[KS]
       const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
       const int i = e >> 1;
       // row_slope: what the score loses per position of distance behind the query (0: nothing; the sum is then exact)
-      const float v = (key >= row_lo[i] && key <= row_hi[i])
+      const float v = ((key >= row_lo[i] || key < keep_first) && key <= row_hi[i])
                           ? fmaf(-row_slope[i], (float)(row_hi[i] - key), s[j][e] * scale_log2) : -INFINITY;
       s[j][e] = v;
       mx[i] = fmaxf(mx[i], v);
@@ -240,12 +240,14 @@ struct PrefillState {
 template <int MTW>
 __device__ __forceinline__ void warp_tile_prefill(PrefillState<MTW>& st, const bf16* qs, int qrow0, const bf16* ks, const bf16* vs,
                                                   int key_base, const int (&row_lo)[MTW][2], const int (&row_hi)[MTW][2],
-                                                  int w_lo, int w_hi, float scale_log2, const float (&row_slope)[MTW][2]) {
+                                                  int w_lo, int w_hi, float scale_log2, const float (&row_slope)[MTW][2],
+                                                  int keep_first) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int kb = h * 32;
-    if (key_base + kb > w_hi || key_base + kb + 32 <= w_lo) continue;      // no row of this warp sees these keys
+    // no row of this warp sees these keys (kept first keys are in sight of every later row)
+    if (key_base + kb > w_hi || (key_base + kb + 32 <= w_lo && key_base + kb >= keep_first)) continue;
     float s[MTW][4][4];
 #pragma unroll
     for (int mt = 0; mt < MTW; ++mt)
@@ -278,7 +280,7 @@ __device__ __forceinline__ void warp_tile_prefill(PrefillState<MTW>& st, const b
         for (int e = 0; e < 4; ++e) {
           const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
           const int i = e >> 1;
-          const float v = (key >= row_lo[mt][i] && key <= row_hi[mt][i])
+          const float v = ((key >= row_lo[mt][i] || key < keep_first) && key <= row_hi[mt][i])
                               ? fmaf(-row_slope[mt][i], (float)(row_hi[mt][i] - key), s[mt][j][e] * scale_log2) : -INFINITY;
           s[mt][j][e] = v;
           mx[i] = fmaxf(mx[i], v);
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
     const bf16* __restrict__ kv_pages, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int nq, int nkv, int page_size,
     int n_pages, int window, int chunk, float scale_log2, int tokens_per_block, const float* __restrict__ sinks,
-    const float* __restrict__ slopes) {
+    const float* __restrict__ slopes, int keep_first) {
   constexpr int PF_ROWS = 64 * MTW;                          // rows (token x head of the group) per block
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qbuf = reinterpret_cast<bf16*>(smem_raw);            // [PF_ROWS rows]
@@ -392,7 +394,12 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
   const int pos_hi = pos0 + tq_n - 1;
   const int first_key = nhv_first_key(pos0, window, chunk);
   const int key_begin = (first_key / BN) * BN;
-  const int n_tiles = (pos_hi - key_begin) / BN + 1;
+  // kept first keys: the tiles that hold keys [0, keep_first) and lie before the window's first tile come first
+  const int keep_tiles = keep_first > 0 ? min((keep_first + BN - 1) / BN, key_begin / BN) : 0;
+  const int n_tiles = keep_tiles + (pos_hi - key_begin) / BN + 1;
+  auto tile_key = [&](int t) { return t < keep_tiles ? t * BN : key_begin + (t - keep_tiles) * BN; };
+  // a tile that holds kept first keys is loaded from its first key on, also where it is the window's first tile
+  auto tile_lo = [&](int t) { return tile_key(t) < keep_first ? 0 : first_key; };
   // this warp's rows: the span of keys any of them sees (warp-uniform, so whole tiles can be skipped)
   const int w_tq_lo = (warp * WROWS) / G, w_tq_hi = min((warp * WROWS + WROWS - 1) / G, tq_n - 1);
   const int w_hi = w_tq_lo < tq_n ? pos0 + w_tq_hi : -1;
@@ -407,26 +414,26 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
 #pragma unroll
     for (int n = 0; n < DN; ++n) st.o[mt][n][0] = st.o[mt][n][1] = st.o[mt][n][2] = st.o[mt][n][3] = 0.f;
   }
-  int page_next = tile_page(geom, key_begin + BN, pos_hi + 1);
-  load_kv_tile(kbuf, vbuf, geom, key_begin, first_key, pos_hi + 1, tile_page(geom, key_begin, pos_hi + 1));
+  int page_next = tile_page(geom, tile_key(1), pos_hi + 1);
+  load_kv_tile(kbuf, vbuf, geom, tile_key(0), tile_lo(0), pos_hi + 1, tile_page(geom, tile_key(0), pos_hi + 1));
   cp_async_commit();
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it & 1;
     if (it + 1 < n_tiles) {
       const int page = page_next;
-      page_next = tile_page(geom, key_begin + (it + 2) * BN, pos_hi + 1);     // looked up one tile ahead
-      load_kv_tile(kbuf + (stage ^ 1) * TILE_ELEMS, vbuf + (stage ^ 1) * TILE_ELEMS, geom, key_begin + (it + 1) * BN,
-                   first_key, pos_hi + 1, page);
+      page_next = tile_page(geom, tile_key(it + 2), pos_hi + 1);              // looked up one tile ahead
+      load_kv_tile(kbuf + (stage ^ 1) * TILE_ELEMS, vbuf + (stage ^ 1) * TILE_ELEMS, geom, tile_key(it + 1),
+                   tile_lo(it + 1), pos_hi + 1, page);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();                                          // also makes the staged queries visible (first pass)
-    const int key_base = key_begin + it * BN;
-    if (key_base <= w_hi && key_base + BN > w_lo)
+    const int key_base = tile_key(it);
+    if (key_base <= w_hi && (key_base + BN > w_lo || key_base < keep_first))
       warp_tile_prefill<MTW>(st, qbuf, warp * WROWS, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, key_base, row_lo,
-                        row_hi, w_lo, w_hi, scale_log2, row_slope);
+                        row_hi, w_lo, w_hi, scale_log2, row_slope, keep_first);
     __syncthreads();
   }
 #pragma unroll
@@ -526,7 +533,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int n_seqs, int nq, int nkv,
     int page_size, int n_pages, int window, int chunk, float scale_log2, int max_pieces, const FusedQK fq,
-    const float* __restrict__ sinks, const float* __restrict__ slopes) {
+    const float* __restrict__ sinks, const float* __restrict__ slopes, int keep_first) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
   bf16* vbuf = kbuf + DSTAGES * TILE_ELEMS;
@@ -553,6 +560,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
       const int total = kv_len[sq];
       const int lo = nhv_first_key(total - 1, window, chunk);
       nt = (total - 1) / BN - lo / BN + 1;
+      if (keep_first > 0) nt += min((keep_first + BN - 1) / BN, lo / BN);      // the kept first keys' tiles come first
     }
     s_cnt[sq] = (unsigned short)min(nt, 65535);
   }
@@ -602,7 +610,10 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     const int gn = min(rows_per, G - g0);
     const int total = kv_len[seq];
     const int lo = nhv_first_key(total - 1, window, chunk);
-    const int key_begin = (lo / BN + t_begin) * BN;
+    const int keep_tiles = keep_first > 0 ? min((keep_first + BN - 1) / BN, lo / BN) : 0;
+    // tile x of this piece: the kept first keys' tiles, then the window's
+    auto tile_key = [&](int x) { const int t = t_begin + x; return t < keep_tiles ? t * BN : (lo / BN + t - keep_tiles) * BN; };
+    auto tile_lo = [&](int x) { return tile_key(x) < keep_first ? 0 : lo; };   // a tile with kept first keys is loaded whole
     const size_t tok = cu_q[seq];
     PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
 
@@ -610,11 +621,11 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
 #pragma unroll
     for (int pre = 0; pre < DSTAGES - 1; ++pre) {
       if (pre < n_tiles)
-        load_kv_tile(kbuf + pre * TILE_ELEMS, vbuf + pre * TILE_ELEMS, geom, key_begin + pre * BN, lo, total,
-                     tile_page(geom, key_begin + pre * BN, total));
+        load_kv_tile(kbuf + pre * TILE_ELEMS, vbuf + pre * TILE_ELEMS, geom, tile_key(pre), tile_lo(pre), total,
+                     tile_page(geom, tile_key(pre), total));
       cp_async_commit();
     }
-    int page_next = tile_page(geom, key_begin + (DSTAGES - 1) * BN, total);
+    int page_next = tile_page(geom, tile_key(DSTAGES - 1), total);
     const bool fused = fq.qkv != nullptr;
     const bool has_last = t_begin + n_tiles == nt;            // this piece ends with the request's newest key
     if (!waited) {
@@ -688,14 +699,14 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
       const int nxt = it + DSTAGES - 1;
       if (nxt < n_tiles) {
         const int page = page_next;
-        page_next = tile_page(geom, key_begin + (nxt + 1) * BN, total);          // looked up one tile ahead
-        load_kv_tile(kbuf + (nxt % DSTAGES) * TILE_ELEMS, vbuf + (nxt % DSTAGES) * TILE_ELEMS, geom, key_begin + nxt * BN,
-                     lo, total, page);
+        page_next = tile_page(geom, tile_key(nxt + 1), total);                   // looked up one tile ahead
+        load_kv_tile(kbuf + (nxt % DSTAGES) * TILE_ELEMS, vbuf + (nxt % DSTAGES) * TILE_ELEMS, geom, tile_key(nxt),
+                     tile_lo(nxt), total, page);
       }
       cp_async_commit();                                       // one group per iteration, empty or not
       cp_async_wait<DSTAGES - 1>();
       __syncthreads();
-      const int key_base = key_begin + it * BN;
+      const int key_base = tile_key(it);
       if (fused && fq.store && has_last && it == n_tiles - 1) {
         // the cache does not hold the newest key and value yet (or is being written): take them from s_new
         const int r = total - 1 - key_base;
@@ -706,8 +717,9 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
         }
         __syncthreads();
       }
-      if (key_base + warp * 16 < total && key_base + warp * 16 + 16 > lo)
-        warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2, row_slope);
+      if (key_base + warp * 16 < total && (key_base + warp * 16 + 16 > lo || key_base + warp * 16 < keep_first))
+        warp_tile<2>(st, qf, kbuf + stage * TILE_ELEMS, vbuf + stage * TILE_ELEMS, warp * 16, key_base, row_lo, row_hi, scale_log2, row_slope,
+                     keep_first);
       __syncthreads();
     }
     cp_async_wait<0>();
@@ -850,7 +862,8 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
                             int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                             int nkv, int page_size, int n_pages, int window, int chunk, float scale, float* scratch_o,
                             float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                            const FusedQK& fq, const float* sinks, const float* slopes, cudaStream_t stream) {
+                            const FusedQK& fq, const float* sinks, const float* slopes, int keep_first, cudaStream_t stream) {
+  ATT_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention: kept first keys go with a window");
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
   ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0 &&
@@ -890,12 +903,12 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
       if (wide)
         nhv_launch(attn_prefill_kernel<2>, grid, THREADS, prefill_smem_bytes<2>(), stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-            n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks, slopes);
+            n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks, slopes, keep_first);
     }
     if (!wide)
       nhv_launch(attn_prefill_kernel<1>, grid, THREADS, prefill_smem_bytes<1>(), stream,
           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-          n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks, slopes);
+          n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks, slopes, keep_first);
   }
   if (n_decode_seqs > 0) {
     ATT_REQUIRE(scratch_o && scratch_ml && counters && max_pieces > 0 && decode_blocks > 0,
@@ -912,7 +925,7 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
     decode_blocks = resident;
     nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, max_pieces, fq, sinks, slopes);
+        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, max_pieces, fq, sinks, slopes, keep_first);
   }
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
@@ -927,11 +940,11 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
                                    int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                                    int nkv, int page_size, int n_pages, int window, int chunk, float scale, float* scratch_o,
                                    float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                                   const float* sinks, const float* slopes, cudaStream_t stream) {
+                                   const float* sinks, const float* slopes, int keep_first, cudaStream_t stream) {
   FusedQK none = {};
   return attention_launch(q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs,
                           n_prefill_tokens, n_prefill_seqs, n_decode_seqs, nq, nkv, page_size, n_pages, window, chunk, scale,
-                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, sinks, slopes, stream);
+                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, sinks, slopes, keep_first, stream);
 }
 
 // 1 if this head size has the form of the decode kernel that works from the projection's output.
@@ -968,5 +981,5 @@ NHV_API int NHV_FN(nhv_attn_mma_decode_fused_d)(const void* qkv, int qkv_stride,
   fq.weight_offset = weight_offset;
   return attention_launch(qkv, qkv_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs, 0, 0,
                           n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale, scratch_o, scratch_ml, counters, max_pieces,
-                          1, fq, nullptr, nullptr, stream);
+                          1, fq, nullptr, nullptr, 0, stream);
 }

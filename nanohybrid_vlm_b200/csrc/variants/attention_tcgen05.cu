@@ -165,6 +165,7 @@ struct alignas(64) Params {
   const float* slopes;    // per query head, or null: the score loses slopes[head] times the distance between query and key
   float inv_scale;        // 1 / scale: the distance term joins the raw score, which the exponent's multiply-add scales
   int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, chunk, tokens_per_block;
+  int keep_first;         // with a window: keys at positions below it stay visible (their tiles come first)
   float scale_log2;
 };
 
@@ -231,7 +232,10 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
   const int pos_hi = pos0 + tq_n - 1;
   const int first_key = nhv_first_key(pos0, p.window, p.chunk);
   const int key_begin = (first_key / BN) * BN;
-  const int n_tiles = active ? (pos_hi - key_begin) / BN + 1 : 0;
+  // kept first keys: the tiles that hold keys [0, keep_first) and lie before the window's first tile come first
+  const int keep_tiles = (active && p.keep_first > 0) ? min((p.keep_first + BN - 1) / BN, key_begin / BN) : 0;
+  const int n_tiles = active ? keep_tiles + (pos_hi - key_begin) / BN + 1 : 0;
+  auto tile_key = [&](int j) { return j < keep_tiles ? j * BN : key_begin + (j - keep_tiles) * BN; };
 
   if (active) {
     // stage Q: row R = token * G + head, 16-byte chunk c of column block b at (c ^ (R & 7)) of the row
@@ -256,12 +260,12 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     if (lane == 0 && n_tiles > 0) {
       const int* bt = p.block_table + (size_t)seq * p.bt_stride;
       int issued = 0;
-      int page = bt[key_begin / p.page_size];
+      int page = bt[tile_key(0) / p.page_size];
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
-        const int key_base = key_begin + j * BN;
+        const int key_base = tile_key(j);
         int page_next = 0;
-        if (j + 1 < n_tiles) page_next = bt[(key_base + BN) / p.page_size];      // looked up one tile ahead
+        if (j + 1 < n_tiles) page_next = bt[tile_key(j + 1) / p.page_size];      // looked up one tile ahead
         const int row_k = ((page * 2) * p.nkv + kvh) * p.page_size + key_base % p.page_size;
         const int row_v = row_k + p.nkv * p.page_size;
         if (j >= STAGES && !mbar_wait(&k_empty[st], (uint32_t)((j >> 1) - 1) & 1, 1)) { *s_abort = 1; break; }
@@ -346,7 +350,7 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     const float slope = (p.slopes && valid) ? p.slopes[kvh * G + g] * p.inv_scale : 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int key_base = key_begin + j * BN;
+      const int key_base = tile_key(j);
       ok = mbar_wait(&s_full[j & 1], (uint32_t)(j >> 1) & 1, 7);
       if (!ok) break;
       tc_fence_after();
@@ -368,7 +372,7 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
 #pragma unroll
         for (int i = 0; i < BN; ++i) {
           const int key = key_base + i;
-          if (!(key >= row_lo && key <= row_hi)) sr[i >> 5][i & 31] = 0xFF800000u;      // -inf
+          if (!((key >= row_lo || key < p.keep_first) && key <= row_hi)) sr[i >> 5][i & 31] = 0xFF800000u;      // -inf
         }
       }
       float mx0 = max3(__uint_as_float(sr[0][0]), __uint_as_float(sr[0][1]), __uint_as_float(sr[0][2]));
@@ -522,7 +526,8 @@ NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, i
                                        const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                                        int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int nq, int nkv,
                                        int page_size, int n_pages, int window, int chunk, float scale, const float* sinks,
-                                       const float* slopes, cudaStream_t stream) {
+                                       const float* slopes, int keep_first, cudaStream_t stream) {
+  ATT_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention: kept first keys go with a window");
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   const int G = nq / nkv;
   ATT_REQUIRE(G <= BM, "attention: a group of %d query heads is beyond the %d rows of a block", G, BM);
@@ -566,6 +571,7 @@ NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, i
   p.n_pages = n_pages;
   p.window = window;
   p.chunk = chunk;
+  p.keep_first = keep_first;
   p.tokens_per_block = BM / G;
   p.scale_log2 = scale * LOG2E;
   const int max_tiles = n_prefill_tokens / p.tokens_per_block + n_prefill_seqs;

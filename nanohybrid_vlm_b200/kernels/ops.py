@@ -801,10 +801,10 @@ def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, 
     than their key heads: picks the kernel for the dtype and sizes.  bfloat16 with key and value heads of one size
     (in steps of 16) runs on the tensor cores like ``attention``; float32 and unequal head sizes on the CUDA cores."""
     if (SINK_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and kv_pages.shape[-1] == dk
-            and kv_pages.shape[1] == 2 and keep_first == 0 and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
+            and kv_pages.shape[1] == 2 and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
         attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
                               batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
-                              nq, nkv, dk, scale, window, sinks, chunk, slopes)
+                              nq, nkv, dk, scale, window, sinks, chunk, slopes, keep_first)
         return
     attention_sink_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
                         nq, nkv, dk, dv, scale, sinks, window, chunk, slopes, keep_first)
@@ -989,14 +989,17 @@ def attention_tcgen05_error(head_dim: int) -> int:
 
 def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_prefill_tokens: int,
                           n_prefill_seqs: int, n_decode_seqs: int, max_kv_len: int, nq: int, nkv: int, head_dim: int,
-                          scale: float, window: int = 0, sinks=None, chunk: int = 0, slopes=None) -> None:
+                          scale: float, window: int = 0, sinks=None, chunk: int = 0, slopes=None, keep_first: int = 0) -> None:
     """bfloat16 attention on the tensor cores.  Prompt portions go to the tcgen05 kernel, requests with
     one new token to the kernel that streams the cache with TMA, each where its shape is supported; what
     neither takes runs in the mma.sync kernel, whose single-token path shares a request's tiles between
     blocks and merges them (scratch: one partial result per piece of a request and head block).
     ``sinks`` [nq] float32: exp(sink) joins each head's softmax denominator once (where the head's sum is final).
     ``slopes`` [nq] float32: head h's score loses slopes[h] times the distance between query and key; the tcgen05 and
-    the mma.sync kernels take them, the TMA kernel for single tokens does not, so those run in the mma.sync kernel."""
+    the mma.sync kernels take them, the TMA kernel for single tokens does not, so those run in the mma.sync kernel.
+    ``keep_first`` > 0 (with a window): the keys at positions below it stay visible; their tiles come before the window's
+    in the tcgen05 and the mma.sync kernels; the TMA kernel for single tokens walks one run of keys, so such tokens run
+    in the mma.sync kernel too."""
     _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks, slopes)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq and sinks.is_contiguous())
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == nq and slopes.is_contiguous())
@@ -1013,11 +1016,12 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
         attention_tcgen05.get(head_dim)[0](
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
-            nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks), _ptr(slopes), stream_ptr())
+            nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks), _ptr(slopes), int(keep_first),
+            stream_ptr())
         if n_decode_seqs == 0:
             return
         n_prefill_tokens = n_prefill_seqs = 0
-    if (n_decode_seqs > 0 and slopes is None and USE_TMA_DECODE
+    if (n_decode_seqs > 0 and slopes is None and keep_first == 0 and USE_TMA_DECODE
             and attention_decode.supports(head_dim, nq, nkv, page_size, n_seqs)):
         # single tokens: the kernel that streams the cache with TMA; what is left for the launch below are the
         # prompt portions (if the tcgen05 kernel did not take them)
@@ -1042,7 +1046,7 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     launch(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
            block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
            n_decode_seqs, nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(scratch_o), _ptr(scratch_ml),
-           _ptr(counters), max_pieces, blocks, _ptr(sinks), _ptr(slopes), stream_ptr())
+           _ptr(counters), max_pieces, blocks, _ptr(sinks), _ptr(slopes), int(keep_first), stream_ptr())
 
 
 _sm_counts: dict = {}

@@ -286,7 +286,11 @@ def random_weights(cfg, seed=0):
             mat(q + "w1", rank, W)
             mat(q + "w2", n, rank, std=0.5)
             vec(q + "w0", n, mean=-1.0, std=1.0)
-            w[q + "u"] = (torch.randn(m["heads"], m["dim"], generator=g) * 0.5).bfloat16().float()
+            # A head's first output is sign(c) v / rms(v) with c = sum_k r_k u_k k_k (the memory is still empty), so a c
+            # near zero would leave the sign to rounding.  Keys that lean on the receptance's projection and a bonus
+            # around one keep c away from zero; nothing else depends on it.
+            w[q + "k"] = (w[q + "r"] + 0.5 * w[q + "k"]).bfloat16().float()
+            w[q + "u"] = (1.0 + torch.randn(m["heads"], m["dim"], generator=g) * 0.3).bfloat16().float()
             vec(q + "norm", n)
             mat(q + "o", W, n)
         mlp = layer.get("mlp")
