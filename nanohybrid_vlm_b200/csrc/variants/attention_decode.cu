@@ -200,9 +200,11 @@ struct RowState {
 };
 
 // One warp, 16 rows, the 32 keys of a tile starting at tile row `kb`: scores, mask, online softmax, P.V.
-// key_base: absolute index of tile row 0.  Row i (0/1) of this thread sees keys in [lo, row_hi[i]].
+// key_base: absolute index of tile row 0.  Row i (0/1) of this thread sees keys in [lo, row_hi[i]] and, of those before,
+// the kept first keys [0, keep_first).
 __device__ __forceinline__ void warp_half_tile(RowState& st, const uint32_t (&qf)[KS][4], const bf16* ks, const bf16* vs,
-                                               int kb, int key_base, int lo, const int (&row_hi)[2], float scale_log2) {
+                                               int kb, int key_base, int lo, const int (&row_hi)[2], float scale_log2,
+                                               int keep_first) {
   const int lane = threadIdx.x & 31;
   constexpr int NT = 4;
   float s[NT][4];
@@ -227,7 +229,7 @@ __device__ __forceinline__ void warp_half_tile(RowState& st, const uint32_t (&qf
       const int key = key_base + kb + 8 * j + ((lane & 3) << 1) + (e & 1);
       const int i = e >> 1;
       // a select, not a sum: whatever a key outside the range holds (stale numbers, NaN) is replaced
-      const float v = (key >= lo && key <= row_hi[i]) ? s[j][e] * scale_log2 : -INFINITY;
+      const float v = ((key >= lo || key < keep_first) && key <= row_hi[i]) ? s[j][e] * scale_log2 : -INFINITY;
       s[j][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -288,6 +290,7 @@ struct alignas(64) Params {
   int* counters;            // [n_seqs * head_blocks], zero; left zero
   const float* sinks;       // per query head, or null: exp(sink) joins the softmax denominator once, where a head's sum is final
   int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, chunk;
+  int keep_first;           // with a window: the keys at positions below it stay visible; their tiles come first
   float scale_log2;
   FusedQK fq;
 };
@@ -359,6 +362,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     if (single) {
       const int lo = nhv_first_key(total - 1, window, chunk);
       nt = total > 0 ? (total - 1) / BN - lo / BN + 1 : 0;
+      if (nt > 0 && p.keep_first > 0) nt += min((p.keep_first + BN - 1) / BN, lo / BN);     // the kept first keys' tiles
       // An entry that only fills the batch up to a fixed shape has no page for its token: it costs nothing here
       // (no tiles, no piece) and its output rows are cleared.
       if (newest < 0 || newest >= p.n_pages) {
@@ -466,12 +470,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       const int kvh = pc.hb / chunks;
       const int total = s_total[pc.seq];
       const int lo = nhv_first_key(total - 1, window, chunk);
-      const int key_begin = (lo / BN + pc.t_begin) * BN;
+      const int keep_tiles = p.keep_first > 0 ? min((p.keep_first + BN - 1) / BN, lo / BN) : 0;
+      const int t_begin = pc.t_begin;
+      // tile x of this piece: the kept first keys' tiles, then the window's
+      auto tile_key = [&](int x) { const int t = t_begin + x; return t < keep_tiles ? t * BN : (lo / BN + t - keep_tiles) * BN; };
       const int* table = p.block_table + (size_t)pc.seq * p.bt_stride;
       for (int it0 = 0; it0 < pc.n_tiles && ok; it0 += 32) {
         int row = 0, there = 0;
         if (it0 + lane < pc.n_tiles) {                       // the pages of 32 tiles at a time
-          const int key0 = key_begin + (it0 + lane) * BN;
+          const int key0 = tile_key(it0 + lane);
           int pg = __ldg(table + key0 / page_size);
           there = pg >= 0 && pg < p.n_pages;
           if (!there) pg = 0;
@@ -532,7 +539,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     const int gn = min(rows_per, G - g0);
     const int total = s_total[seq];
     const int lo = nhv_first_key(total - 1, window, chunk);
-    const int key_begin = (lo / BN + pc.t_begin) * BN;
+    const int keep_first = p.keep_first;
+    const int keep_tiles = keep_first > 0 ? min((keep_first + BN - 1) / BN, lo / BN) : 0;
+    const int t_begin = pc.t_begin;
+    auto tile_key = [&](int x) { const int t = t_begin + x; return t < keep_tiles ? t * BN : (lo / BN + t - keep_tiles) * BN; };
     const size_t tok = s_tok[seq];
     const bool has_last = pc.t_begin + n_tiles == nt;         // this piece ends with the request's newest key
     if (!waited) {
@@ -620,7 +630,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       if (!ok) break;
       bf16* kt = reinterpret_cast<bf16*>(ring + (size_t)stage * STAGE_BYTES);
       bf16* vt = reinterpret_cast<bf16*>(ring + (size_t)stage * STAGE_BYTES + TILE_BYTES);
-      const int key_base = key_begin + it * BN;
+      const int key_base = tile_key(it);
       const bool there = s_tile_ok[stage] != 0;
       bool wrote = false;
       if (fused && fq.store && has_last && it == n_tiles - 1) {
@@ -636,17 +646,18 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       // (stale numbers, NaN of a fresh pool) must be zero too
       const int r_lo = there ? min(BN, max(0, lo - key_base)) : BN;            // rows [0, r_lo) are before the range
       const int r_hi = there ? min(BN, max(0, total - key_base)) : BN;         // rows [r_hi, BN) are beyond it
-      if (r_lo > 0 || r_hi < BN) {
+      const int r_keep = there ? min(BN, max(0, keep_first - key_base)) : 0;   // rows [0, r_keep) are kept first keys
+      if (r_lo > r_keep || r_hi < BN) {
         for (int id = lane; id < BN * CH; id += 32) {
           const int r = id / CH, cc = id - r * CH;
-          if (r < r_lo || r >= r_hi) *reinterpret_cast<uint4*>(vt + tile_off<BN>(r, cc)) = make_uint4(0, 0, 0, 0);
+          if ((r < r_lo && r >= r_keep) || r >= r_hi) *reinterpret_cast<uint4*>(vt + tile_off<BN>(r, cc)) = make_uint4(0, 0, 0, 0);
         }
         wrote = true;
       }
       if (wrote) __syncwarp();
       const int lo_t = there ? lo : 0x7fffffff;               // a tile whose page is missing: no key counts
-      if (key_base < total && key_base + BN > lo_t)
-        warp_half_tile(st, qf, kt, vt, 0, key_base, lo_t, row_hi, p.scale_log2);
+      if (key_base < total && (key_base + BN > lo_t || (there && key_base < keep_first)))
+        warp_half_tile(st, qf, kt, vt, 0, key_base, lo_t, row_hi, p.scale_log2, there ? keep_first : 0);
       if (wrote) fence_async_smem();                          // this warp's stores before the next copy into the stage
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
@@ -814,7 +825,8 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
                                       int window, int chunk, float scale, float* part_o, float* part_ml, int* counters,
                                       const void* q_w, const void* k_w, const float* cos_sin, const int* positions,
                                       const int* slot_mapping, int rotary_dim, int max_position, int store, float eps,
-                                      float weight_offset, const float* sinks, cudaStream_t stream) {
+                                      float weight_offset, const float* sinks, int keep_first, cudaStream_t stream) {
+  ATT_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0), "attention: kept first keys go with a window");
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && page_size % BN == 0 && n_pages > 0 && bt_stride > 0,
               "attention (decode, TMA): pages must be a multiple of %d keys, got %d", BN, page_size);
@@ -893,7 +905,7 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
   p.counters = counters;
   p.sinks = sinks;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv;
-  p.page_size = page_size; p.n_pages = n_pages; p.window = window; p.chunk = chunk;
+  p.page_size = page_size; p.n_pages = n_pages; p.window = window; p.chunk = chunk; p.keep_first = keep_first;
   p.scale_log2 = scale * LOG2E;
   const cudaError_t launched = deep ? nhv_launch(attn_decode_kernel<STAGES_DEEP, 8>, dim3(blocks), dim3(THREADS), smem, stream, p)
                                     : nhv_launch(attn_decode_kernel<STAGES_MIN, 16>, dim3(blocks), dim3(THREADS), smem, stream, p);

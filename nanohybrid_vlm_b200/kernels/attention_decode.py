@@ -31,7 +31,7 @@ def get(head_dim: int):
         from ..csrc.build import ensure_variant
         lib = ctypes.CDLL(ensure_variant("attention_decode.cu", {"NHV_ATTN_D": head_dim}))
         fn = getattr(lib, f"nhv_attn_decode_d{head_dim}")
-        fn.argtypes = [P, I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, I, I, F, F, P, P]
+        fn.argtypes = [P, I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, I, I, F, F, P, I, P]
         fn.restype = c_int
         err = getattr(lib, f"nhv_attn_decode_last_error_d{head_dim}")
         err.restype = ctypes.c_char_p

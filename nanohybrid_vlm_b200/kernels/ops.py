@@ -916,7 +916,8 @@ def _tma_decode_scratch(device, head_dim: int, blocks: int):
 def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_kv_len, n_seqs: int, nq: int, nkv: int,
                           head_dim: int, scale: float, window: int, q_weight=None, k_weight=None, cos_sin=None,
                           positions=None, slot_mapping=None, rotary_dim: int = 0, eps: float = 0.0,
-                          weight_offset: float = 0.0, store: bool = False, sinks=None, chunk: int = 0) -> None:
+                          weight_offset: float = 0.0, store: bool = False, sinks=None, chunk: int = 0,
+                          keep_first: int = 0) -> None:
     launch, blocks = attention_decode.get(head_dim)
     n_pages, two, h, page_size, d = kv_pages.shape
     group = nq // nkv
@@ -929,7 +930,7 @@ def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_
            batch_kv_len.data_ptr(), n_seqs, nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), part_o.data_ptr(),
            part_ml.data_ptr(), counters.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), _ptr(positions),
            _ptr(slot_mapping), int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0], 1 if store else 0, float(eps),
-           float(weight_offset), _ptr(sinks), stream_ptr())
+           float(weight_offset), _ptr(sinks), int(keep_first), stream_ptr())
 
 
 def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float,
@@ -997,9 +998,8 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     ``sinks`` [nq] float32: exp(sink) joins each head's softmax denominator once (where the head's sum is final).
     ``slopes`` [nq] float32: head h's score loses slopes[h] times the distance between query and key; the tcgen05 and
     the mma.sync kernels take them, the TMA kernel for single tokens does not, so those run in the mma.sync kernel.
-    ``keep_first`` > 0 (with a window): the keys at positions below it stay visible; their tiles come before the window's
-    in the tcgen05 and the mma.sync kernels; the TMA kernel for single tokens walks one run of keys, so such tokens run
-    in the mma.sync kernel too."""
+    ``keep_first`` > 0 (with a window): the keys at positions below it stay visible; in every kernel their tiles come
+    before the window's."""
     _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks, slopes)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq and sinks.is_contiguous())
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == nq and slopes.is_contiguous())
@@ -1021,12 +1021,12 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
         if n_decode_seqs == 0:
             return
         n_prefill_tokens = n_prefill_seqs = 0
-    if (n_decode_seqs > 0 and slopes is None and keep_first == 0 and USE_TMA_DECODE
+    if (n_decode_seqs > 0 and slopes is None and USE_TMA_DECODE
             and attention_decode.supports(head_dim, nq, nkv, page_size, n_seqs)):
         # single tokens: the kernel that streams the cache with TMA; what is left for the launch below are the
         # prompt portions (if the tcgen05 kernel did not take them)
         _attention_decode_tma(out, q, None, kv_pages, block_table, cu_q, kv_len, n_seqs, nq, nkv, head_dim, scale, window,
-                              sinks=sinks, chunk=chunk)
+                              sinks=sinks, chunk=chunk, keep_first=keep_first)
         if n_prefill_tokens == 0:
             return
         n_decode_seqs = 0

@@ -340,7 +340,8 @@ def plain_heads(q, k, v, nq, nkv, scale, window, keep_first, extra_one):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("simt", [True, False], ids=["cuda_cores", "dispatcher"])
 @pytest.mark.parametrize("nq,nkv,d,page,window,keep", [(4, 2, 16, 8, 24, 5), (6, 3, 128, 16, 96, 6), (2, 2, 64, 16, 40, 33),
-                                                       (8, 1, 64, 64, 70, 64), (3, 1, 48, 16, 10, 17), (6, 3, 128, 16, 32, 0)])
+                                                       (8, 1, 64, 64, 70, 64), (3, 1, 48, 16, 10, 17), (6, 3, 128, 16, 32, 0),
+                                                       (4, 2, 128, 64, 96, 6), (2, 1, 64, 128, 130, 70)])
 def test_attention_kernels_keep_first_keys(ops, dtype, simt, nq, nkv, d, page, window, keep, monkeypatch):
     """The attention kernels with kept first keys, in portions and single tokens over a cache whose pages between the kept
     keys and the window are gone (NaN in the pool).  Planted: some queries would, but for the mask, give nearly all
