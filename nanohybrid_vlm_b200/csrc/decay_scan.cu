@@ -13,17 +13,16 @@
 // decay_lowrank: w[t, c] = exp(-exp(w0[c] + sum_j tanh(inner[t, j]) w2[c, j])), the decay of the first form from the
 // fp32 sums of its inner projection; the tanh stays fp32 and the small second product is summed in fp32 in a fixed order.
 //
-// Block = (request, head, 16 columns of the state); a column lives in 8 lanes, lane l holding the key channels
-// 32 i + 4 l .. + 3 of it in registers (KPL channels per lane).  Tokens are staged 16 at a time in shared memory (8 for the widest heads).
+// Block = (request, head, 16 columns of the state); a column lives in 8 lanes (heads of up to 32 key channels) or 16,
+// lane l holding the key channels 4 LANES i + 4 l .. + 3 of it in registers (KPL channels per lane).  Tokens are staged
+// 16 at a time in shared memory (8 for the widest heads).
 // State layout per slot: [H][dv][dk].  A request with q_start == 0 starts from zeros whatever its slot held; a request
 // without a slot (slot < 0: the idle entries that pad a captured batch) gets zeros and keeps nothing.
 #include <math.h>
 
 #include "nhv_common.cuh"
 
-constexpr int DS_THREADS = 128;
-constexpr int DS_LANES = 8;
-constexpr int DS_COLS = DS_THREADS / DS_LANES;
+constexpr int DS_COLS = 16;          // columns of the memory per block
 constexpr int DS_TOKENS = 16;
 
 // 16 bytes of the storage type, kept as they were read until they are needed (a register that is only the target of a
@@ -67,20 +66,22 @@ template <typename T> __device__ __forceinline__ float ds_silu(float x) {
 // layout allows; issued before the chunk in shared memory is worked on, so the reads are in flight meanwhile), `put`
 // writes it, widened and through SiLU if asked, into shared memory.
 // CW: the decay is one constant per head (it is not staged per token and key channel).
-template <typename T, int KPL, bool CW>
-__global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
+// LANES: lanes that share a column (8 or 16); the block has DS_COLS * LANES threads.
+template <typename T, int KPL, int LANES, bool CW>
+__global__ void __launch_bounds__(DS_COLS * LANES) decay_scan_kernel(
     float* __restrict__ o, const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int ld,
     const float* __restrict__ w_tok, const float* __restrict__ w_head, const T* __restrict__ bonus,
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
     const int* __restrict__ slots, int H, int dk, int dv, int act_silu, int read_after, int vec_ok, int wvec_ok) {
+  constexpr int DS_THREADS = DS_COLS * LANES, DS_LANES = LANES;
   constexpr int DKP = KPL * DS_LANES;                 // key channels with padding (zeros)
-  constexpr int TOK = KPL >= 32 ? DS_TOKENS / 2 : DS_TOKENS;      // the widest heads stage fewer tokens (48 KB of static shared memory)
+  constexpr int TOK = DKP >= 256 ? DS_TOKENS / 2 : DS_TOKENS;     // the widest heads stage fewer tokens (48 KB of static shared memory)
   constexpr int VN = DsVec<T>::N;
   constexpr int RK_VECS = TOK * DKP / VN;             // 16-byte pieces of r (and of k) in a chunk
   constexpr int RK_PER = (RK_VECS + DS_THREADS - 1) / DS_THREADS;
   constexpr int W_VECS = TOK * DKP / 4;               // float4 pieces of the decay in a chunk
   constexpr int W_PER = (W_VECS + DS_THREADS - 1) / DS_THREADS;
-  constexpr int V_PER = TOK * DS_COLS / DS_THREADS;
+  constexpr int V_PER = (TOK * DS_COLS + DS_THREADS - 1) / DS_THREADS;
   __shared__ __align__(16) float rs[TOK][DKP];
   __shared__ __align__(16) float ks[TOK][DKP];
   __shared__ __align__(16) float ws[TOK][DKP];
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
   float* st = slot >= 0 ? state + (size_t)slot * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk : nullptr;
 #pragma unroll
   for (int i = 0; i < KPL; ++i) {
-    const int c = (i >> 2) * 32 + lane * 4 + (i & 3);
+    const int c = (i >> 2) * (4 * DS_LANES) + lane * 4 + (i & 3);
     S[i] = (st && col_ok && c < dk && q_start[seq] > 0) ? st[c] : 0.f;
   }
   const float wh = w_head ? w_head[h] : 1.f;
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     for (int q = 0; q < V_PER; ++q) {
       const int idx = tid + q * DS_THREADS;
       const int tt = idx / DS_COLS, c = idx - tt * DS_COLS;
-      fv[q] = (tt < nt && col0 + c < dv) ? v[(size_t)(first + t0 + tt) * ld + (size_t)h * dv + col0 + c] : from_f32<T>(0.f);
+      fv[q] = (idx < TOK * DS_COLS && tt < nt && col0 + c < dv) ? v[(size_t)(first + t0 + tt) * ld + (size_t)h * dv + col0 + c] : from_f32<T>(0.f);
     }
   };
   auto put = [&]() {
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
       const int idx = tid + q * DS_THREADS;
       const int tt = idx / DS_COLS, c = idx - tt * DS_COLS;
       const float x = to_f32<T>(fv[q]);
-      vs[tt][c] = act_silu ? ds_silu<T>(x) : x;
+      if (idx < TOK * DS_COLS) vs[tt][c] = act_silu ? ds_silu<T>(x) : x;
     }
   };
   // the bonus of this lane's key channels in the per-token sums below (ones where there is none)
@@ -225,10 +226,10 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
       for (int j = 0; j < KPL / 4; ++j) {
-        const float4 r4 = *reinterpret_cast<const float4*>(&rs[tt][j * 32 + lane * 4]);
-        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][j * 32 + lane * 4]);
+        const float4 r4 = *reinterpret_cast<const float4*>(&rs[tt][j * (4 * DS_LANES) + lane * 4]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][j * (4 * DS_LANES) + lane * 4]);
         // (padded key channels decay by the constant too: their memory is zero and their keys are zero)
-        const float4 w4 = CW ? make_float4(wh, wh, wh, wh) : *reinterpret_cast<const float4*>(&ws[tt][j * 32 + lane * 4]);
+        const float4 w4 = CW ? make_float4(wh, wh, wh, wh) : *reinterpret_cast<const float4*>(&ws[tt][j * (4 * DS_LANES) + lane * 4]);
         acc0 = fmaf(r4.x, S[4 * j + 0], acc0);
         acc1 = fmaf(r4.y, S[4 * j + 1], acc1);
         acc0 = fmaf(r4.z, S[4 * j + 2], acc0);
@@ -239,6 +240,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
         S[4 * j + 3] = fmaf(w4.w, S[4 * j + 3], k4.w * vt);
       }
       float acc = acc0 + acc1;
+      if (DS_LANES == 16) acc += __shfl_xor_sync(0xffffffffu, acc, 8);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
   if (st && col_ok) {
 #pragma unroll
     for (int i = 0; i < KPL; ++i) {
-      const int c = (i >> 2) * 32 + lane * 4 + (i & 3);
+      const int c = (i >> 2) * (4 * DS_LANES) + lane * 4 + (i & 3);
       if (c < dk) st[c] = S[i];
     }
   }
@@ -268,21 +270,22 @@ NHV_API int nhv_decay_scan(int dtype, float* o, const void* r, const void* k, co
   const int per16 = (int)(16 / esize);
   const int vec_ok = ld % per16 == 0 && dk % per16 == 0 && ((uintptr_t)r % 16) == 0 && ((uintptr_t)k % 16) == 0;
   const int wvec_ok = w_tok && dk % 4 == 0 && ((uintptr_t)w_tok % 16) == 0;
-#define LAUNCH(T, KPL)                    \
-  do {                                    \
-    if (w_head) LAUNCH_W(T, KPL, true);   \
-    else LAUNCH_W(T, KPL, false);         \
+#define LAUNCH(T, KPL, LANES)                    \
+  do {                                           \
+    if (w_head) LAUNCH_W(T, KPL, LANES, true);   \
+    else LAUNCH_W(T, KPL, LANES, false);         \
   } while (0)
-#define LAUNCH_W(T, KPL, CW)                                                                                         \
-  nhv_launch(decay_scan_kernel<T, KPL, CW>, grid, DS_THREADS, 0, stream, o, (const T*)r, (const T*)k, (const T*)v, ld, \
+#define LAUNCH_W(T, KPL, LANES, CW)                                                                                  \
+  nhv_launch(decay_scan_kernel<T, KPL, LANES, CW>, grid, DS_COLS * LANES, 0, stream, o, (const T*)r, (const T*)k,    \
+             (const T*)v, ld,                                                                                        \
              w_tok, w_head, (const T*)bonus, state, state_stride, cu_q, q_start, slots, H, dk, dv, act_silu, read_after,  \
              vec_ok, wvec_ok)
 #define LAUNCH_K(T)                    \
   do {                                 \
-    if (dk <= 32) LAUNCH(T, 4);        \
-    else if (dk <= 64) LAUNCH(T, 8);   \
-    else if (dk <= 128) LAUNCH(T, 16); \
-    else LAUNCH(T, 32);                \
+    if (dk <= 32) LAUNCH(T, 4, 8);          \
+    else if (dk <= 64) LAUNCH(T, 4, 16);    \
+    else if (dk <= 128) LAUNCH(T, 8, 16);   \
+    else LAUNCH(T, 16, 16);                 \
   } while (0)
   if (dtype == NHV_F32) LAUNCH_K(float);
   else if (dtype == NHV_BF16) LAUNCH_K(__nv_bfloat16);

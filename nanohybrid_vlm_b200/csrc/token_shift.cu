@@ -1,6 +1,6 @@
 // Mixes of a token's input with the input of the token before it, for packed steps of several requests:
 //
-//   out[t, s, c] = x[t, c] + (x[t - 1, c] - x[t, c]) * mu[s, c]        s < n_mix
+//   out[s, t, c] = x[t, c] + (x[t - 1, c] - x[t, c]) * mu[s, c]        s < n_mix  (one contiguous [T, C] plane per mix)
 //
 // where t counts within the request: the token before a request's first token is zero, and the one before this step's
 // portion is the request's state (fp32, [slot][C]: its last input).  A first kernel computes all mixes (reading the
@@ -47,10 +47,10 @@ __global__ void token_shift_mix_kernel(T* __restrict__ out, const T* __restrict_
     }
     const float xt = to_f32<T>(x[(size_t)t * C + c]);
     const float d = prev - xt;
-    T* dst = out + ((size_t)t * n_mix) * C + c;
+    T* dst = out + (size_t)t * C + c;
 #pragma unroll
     for (int k = 0; k < TS_MAX_MIX; ++k)
-      if (k < n_mix) dst[(size_t)k * C] = from_f32<T>(fmaf(d, m[k], xt));
+      if (k < n_mix) dst[(size_t)k * n_tokens * C] = from_f32<T>(fmaf(d, m[k], xt));
     prev = xt;
   }
 }

@@ -470,13 +470,14 @@ def stream_round(out, stream) -> None:
 
 
 def token_shift_mix(out, x, mu, state, batch) -> None:
-    """out [T, n, C]: out[t, s] = x[t] + (x[t - 1] - x[t]) * mu[s] for mu [n, C]; the token before a request's first
-    is zero, the one before this step's portion is the request's ``state`` [slots, C] float32, which is moved on."""
+    """out [n, T, C]: out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] for mu [n, C] (one contiguous plane per mix, so that
+    each is a product's operand as it lies); the token before a request's first is zero, the one before this step's
+    portion is the request's ``state`` [slots, C] float32, which is moved on."""
     _need_cuda(out, x, mu, state)
     _contig("out", out); _contig("x", x); _contig("mu", mu)
     T, C = x.shape
     n = mu.shape[0]
-    assert out.shape == (T, n, C) and mu.shape == (n, C) and out.dtype == x.dtype == mu.dtype
+    assert out.shape == (n, T, C) and mu.shape == (n, C) and out.dtype == x.dtype == mu.dtype
     assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= C
     call("nhv_token_shift_mix", dtype_code(x), out.data_ptr(), x.data_ptr(), mu.data_ptr(), state.data_ptr(), state.stride(0),
          batch.cu_q.data_ptr(), batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, C, n, stream_ptr())

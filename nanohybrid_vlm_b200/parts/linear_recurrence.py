@@ -67,20 +67,19 @@ class WKV(Mixer):
     def forward(self, x, batch, cache):
         T, n, W = x.shape[0], self.n, self.env.hidden_size
         last_input, memory = cache.children[0].state, cache.children[1].state
-        mixes = self.new(T, len(MIXES), W)
+        mixes = self.new(len(MIXES), T, W)              # one contiguous plane per mix
         ops.token_shift_mix(mixes, x, self.w_mu, last_input, batch)
-        proj = self.new(T, 4, n)
-        ops.linear_heads(proj, mixes[:, :4], self.w_rkvg)
+        proj = self.new(4, T, n)                        # r, k, v, g: four products in one batched launch
+        ops.linear_heads(proj.transpose(0, 1), mixes[:4].transpose(0, 1), self.w_rkvg)
         inner = self.new(T, self.rank, dtype=torch.float32)
-        ops.linear_f32(inner, mixes[:, 4], self.w_w1)
+        ops.linear_f32(inner, mixes[4], self.w_w1)
         decay = self.new(T, n, dtype=torch.float32)
         ops.decay_lowrank(decay, inner, self.w_w2, self.w_w0)
         o = self.new(T, n, dtype=torch.float32)
-        flat = proj.view(T, 4 * n)
-        ops.decay_scan(o, flat[:, :n], flat[:, n:2 * n], flat[:, 2 * n:3 * n], memory, batch, self.H, self.d, self.d,
-                       decay_tokens=decay, bonus=self.w_u)
+        ops.decay_scan(o, proj[0], proj[1], proj[2], memory, batch, self.H, self.d, self.d, decay_tokens=decay,
+                       bonus=self.w_u)
         gated = self.new(T, n)
-        ops.gated_rmsnorm(gated, o, flat[:, 3 * n:], self.w_norm, self.H, self.eps, gate_first=False, gate="silu")
+        ops.gated_rmsnorm(gated, o, proj[3], self.w_norm, self.H, self.eps, gate_first=False, gate="silu")
         out = self.new(T, W)
         ops.linear(out, gated, self.w_o)
         return out

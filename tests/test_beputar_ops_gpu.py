@@ -241,11 +241,11 @@ def test_token_shift_mixes_with_reused_slots(ops, dtype, width, n_mix):
         starts = [bounds[r][progress[r]] for r in who]
         news = [bounds[r][progress[r] + 1] - s for r, s in zip(who, starts)]
         x = torch.cat([xs[r][s:s + n] for r, s, n in zip(who, starts, news)])
-        out = torch.empty(x.shape[0], n_mix, width, dtype=dtype, device="cuda")
+        out = torch.empty(n_mix, x.shape[0], width, dtype=dtype, device="cuda")
         ops.token_shift_mix(out, dev(x), dev(mu), state, step_batch(news, starts, [slot_of[r] for r in who]))
         at = 0
         for r, s, n in zip(who, starts, news):
-            got[r].append(out[at:at + n].cpu())
+            got[r].append(out[:, at:at + n].transpose(0, 1).cpu())
             at += n
             progress[r] += 1
             if s + n == LENGTHS[r]:
