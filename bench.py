@@ -787,7 +787,11 @@ def bench_designs(args) -> dict:
         runner = llm.model_runner
         weights = sum(bp.decl.shape[0] * bp.decl.shape[1] for bp in runner.model.param_table() if len(bp.decl.shape) == 2)
         # stacks of experts [E, rows, columns]: a token uses `top` of the E (fewer where it chooses identity experts)
-        stacks = [bp.decl.shape for bp in runner.model.param_table() if len(bp.decl.shape) == 3]
+        stacks = [bp.decl.shape for bp in runner.model.param_table() if len(bp.decl.shape) == 3 and bp.owner.spec.kind == "routed_moe"]
+        # other stacks (several products with several inputs in one launch) are read whole by every token
+        weights_2d = weights
+        weights += sum(a * r * c for bp in runner.model.param_table() if len(bp.decl.shape) == 3
+                       and bp.owner.spec.kind != "routed_moe" for a, r, c in [bp.decl.shape])
         expert_weights = sum(e * r * c for e, r, c in stacks)
         tops = [dict(lay.ffn.spec.items) for lay in runner.model.spec.layers if "ffn" in dict(lay.parts)
                 and lay.ffn.spec.kind == "routed_moe"]
@@ -842,7 +846,7 @@ def bench_designs(args) -> dict:
                "prefill_ms": round(prefill_ms, 3),
                "prefill_tok_s": round(T / prefill_ms * 1e3),
                "prefill_us_by_kind": {k: round(v, 1) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])}}
-        gemm_flops = 2.0 * T * (weights - vocab * cfg.get("width", cfg.get("hidden_size")))
+        gemm_flops = 2.0 * T * (weights_2d - vocab * cfg.get("width", cfg.get("hidden_size")))
         if "gemm" in by_kind:
             out["gemm_frac_of_measured_bf16"] = round(gemm_flops / (by_kind["gemm"] * 1e-6) / (pk["bf16_tflops"] * 1e12), 3)
         if "experts" in by_kind:     # an upper bound of the work: every choice counted as a real expert
