@@ -712,12 +712,12 @@ def beputar_config(width: int, heads: int, ff: int, layers: int) -> dict:
     moe = dict(kind="moe", router=dict(experts=16, top=4), expert=dict(ff=ff * 2 // 11), shared=dict(ff=ff * 3 // 11))
     kv = max(heads // 4, 1)
     pair = dict(type="parallel", mixer=dict(
-        left=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, rot=dict(base=500000.0, dims=64),
+        left=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, rot=dict(base=1000000.0, dims=64),
                   mask=dict(size=1024, keep_first=4)),
         right=dict(heads=heads // 2, dim=128, vdim=128, decay=[1.0 - 2.0 ** -(5 + 3 * h / max(heads // 2 - 1, 1)) for h in range(heads // 2)])))
     attention = dict(type="attention", mixer=dict(
         heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=4096),
-        rot=dict(base=50000.0, dims=128, scaling=dict(factor=4.0, original=1024, fast=32.0, slow=1.0))))
+        rot=dict(base=200000.0, dims=128, scaling=dict(factor=8.0, original=4096, fast=16.0, slow=2.0))))
     mixing = dict(type="wkv", mixer=dict(heads=width // 64, dim=64, decay_rank=64))
     kinds = [dict(pair, mlp=dict(kind="dense", ff=ff)), dict(attention, mlp=moe), dict(mixing, mlp=moe), dict(pair, mlp=moe)]
     return dict(architecture="Beputar", vocab=DESIGN_VOCAB, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-6),
